@@ -1,0 +1,120 @@
+"""ctypes binding of the C ABI in ``include/ms_blkq4gemm.h``.
+
+Arguments are raw device pointers (ints) and byte sizes, exactly as a C caller
+would pass them; torch tensors are accepted for convenience and contribute their
+``data_ptr()`` / byte size only.  Errors raise :class:`BlkQ4Error` carrying the
+library's message.  Nothing here computes anything: if the shared library is
+missing this module raises at import time.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libms_blkq4gemm.so")
+
+SYMBOLS = (
+    "blkq4_fp16_gemm_sm80",
+    "blkq4_fp16_quant_sm80",
+    "blkq4_fp16_quant_size_sm80",
+    "blkq4_errmsg_create",
+    "blkq4_errmsg_cstr",
+    "blkq4_errmsg_destroy",
+    "blkq4_version",
+)
+
+
+class BlkQ4Error(RuntimeError):
+    pass
+
+
+def _load() -> ctypes.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m gemmlib_b200.build` "
+            "(there is no fallback implementation)"
+        )
+    lib = ctypes.CDLL(LIB_PATH)
+    vp, sz, i, b = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_bool
+    lib.blkq4_fp16_gemm_sm80.argtypes = [i, b, i, i, i, vp, vp, sz, vp, sz, vp, sz, vp, sz, vp, sz, vp]
+    lib.blkq4_fp16_gemm_sm80.restype = i
+    lib.blkq4_fp16_quant_sm80.argtypes = [i, b, i, i, i, vp, vp, sz, vp, sz, vp, sz, vp, sz, vp]
+    lib.blkq4_fp16_quant_sm80.restype = i
+    i64p = ctypes.POINTER(ctypes.c_int64)  # int64_t& is passed as a pointer
+    lib.blkq4_fp16_quant_size_sm80.argtypes = [i, b, i, i, i64p, i64p, vp]
+    lib.blkq4_fp16_quant_size_sm80.restype = i
+    lib.blkq4_errmsg_create.restype = vp
+    lib.blkq4_errmsg_cstr.argtypes = [vp]
+    lib.blkq4_errmsg_cstr.restype = ctypes.c_char_p
+    lib.blkq4_errmsg_destroy.argtypes = [vp]
+    lib.blkq4_version.restype = ctypes.c_char_p
+    return lib
+
+
+lib = _load()
+
+
+class _ErrMsg:
+    def __enter__(self):
+        self.p = lib.blkq4_errmsg_create()
+        return self
+
+    def __exit__(self, *exc):
+        lib.blkq4_errmsg_destroy(self.p)
+
+    def text(self) -> str:
+        return lib.blkq4_errmsg_cstr(self.p).decode()
+
+
+def _ptr_size(t):
+    """(device pointer, byte size) of a torch tensor, or (0, 0) for None."""
+    if t is None:
+        return 0, 0
+    if isinstance(t, tuple):
+        return int(t[0]), int(t[1])
+    n = t.numel() * t.element_size()
+    return (t.data_ptr() if n else 0), n
+
+
+def version() -> str:
+    return lib.blkq4_version().decode()
+
+
+def quant_size(block_size: int, column_wise: bool, rows: int, columns: int):
+    """-> (quant weight bytes, meta element count)."""
+    w, m = ctypes.c_int64(0), ctypes.c_int64(0)
+    with _ErrMsg() as e:
+        rc = lib.blkq4_fp16_quant_size_sm80(
+            block_size, column_wise, rows, columns, ctypes.byref(w), ctypes.byref(m), e.p
+        )
+        if rc != 0:
+            raise BlkQ4Error(e.text())
+    return w.value, m.value
+
+
+def quant(block_size, column_wise, rows, columns, ld, weights, q_weights, q_scales, q_zp, stream=0):
+    wp, ws = _ptr_size(weights)
+    qp, qs = _ptr_size(q_weights)
+    sp, ss = _ptr_size(q_scales)
+    zp, zs = _ptr_size(q_zp)
+    with _ErrMsg() as e:
+        rc = lib.blkq4_fp16_quant_sm80(
+            block_size, column_wise, rows, columns, ld, stream, wp, ws, qp, qs, sp, ss, zp, zs, e.p
+        )
+        if rc != 0:
+            raise BlkQ4Error(e.text())
+
+
+def gemm(block_size, column_wise, m, n, k, act, q_weights, q_scales, q_zp, out, stream=0):
+    ap, as_ = _ptr_size(act)
+    qp, qs = _ptr_size(q_weights)
+    sp, ss = _ptr_size(q_scales)
+    zp, zs = _ptr_size(q_zp)
+    op, os_ = _ptr_size(out)
+    with _ErrMsg() as e:
+        rc = lib.blkq4_fp16_gemm_sm80(
+            block_size, column_wise, m, n, k, stream, ap, as_, qp, qs, sp, ss, zp, zs, op, os_, e.p
+        )
+        if rc != 0:
+            raise BlkQ4Error(e.text())

@@ -1,0 +1,164 @@
+// extern "C" entry points of the blockwise-int4 GEMM library (sm_100a build):
+// argument validation and dispatch.  Validation rules and error texts follow the
+// reference dispatcher, src/blkq4_f16_gemm_sm80.cu:38-153 (GEMM), :155-203 (size
+// query), :205-314 (quantize) and :319-531 (the extern "C" switches).
+#include <cstddef>
+#include <cstdint>
+#include <string>
+
+#include "blkq4_common.cuh"
+#include "ms_blkq4gemm.h"
+
+namespace {
+
+inline int fail(void* err, const std::string& msg) {
+  if (err) *reinterpret_cast<std::string*>(err) = msg;
+  return -1;
+}
+
+// Reference: blkq4_quant_size_sm80_T, src/blkq4_f16_gemm_sm80.cu:155-203.
+// The reference tests divisibility as "rows % meta_rows" / "columns % meta_cols",
+// which accepts shapes whose last block is partial (e.g. 96 columns, row-wise
+// block 64) and then indexes meta out of bounds in its quantize kernel.  Whole
+// blocks are required here instead; every shape the reference handles correctly
+// is still accepted.
+int quant_size(int block, bool colwise, int rows, int columns, int64_t& wsz, int64_t& msz,
+               void* err) {
+  if (!blkq4::supported_block(block))
+    return fail(err, "Unsupported block size: " + std::to_string(block));
+  if (rows <= 0 || columns <= 0)
+    return fail(err, "Empty problem size: " + std::to_string(rows) + "x" + std::to_string(columns));
+  const blkq4::Blocking b(block, colwise);
+  if ((rows % 64) != 0 || (rows % b.bk) != 0)
+    return fail(err, "Cannot block quantize matrix with rows: " + std::to_string(rows));
+  if ((columns % 32) != 0 || (columns % b.bn) != 0)
+    return fail(err, "Cannot block quantize matrix with columns: " + std::to_string(columns));
+  wsz = (int64_t)(rows / 2) * columns;
+  msz = (int64_t)(rows / b.bk) * (columns / b.bn);
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int blkq4_fp16_quant_size_sm80(int block_size, bool column_wise_blocking, int rows,
+                                          int columns, int64_t& quant_weights_size,
+                                          int64_t& quant_meta_size, void* error_message) {
+  quant_weights_size = 0;
+  quant_meta_size = 0;
+  return quant_size(block_size, column_wise_blocking, rows, columns, quant_weights_size,
+                    quant_meta_size, error_message);
+}
+
+extern "C" int blkq4_fp16_quant_sm80(int block_size, bool column_wise_blocking, int rows,
+                                     int columns, int leadingDimension, void* stream_ptr,
+                                     void const* weights, size_t weights_size,
+                                     void* quant_weights, size_t quant_weights_size,
+                                     void* quant_scales, size_t quant_scales_size, void* offsets,
+                                     size_t offsets_size, void* err) {
+  int64_t wsz = 0, msz = 0;
+  if (quant_size(block_size, column_wise_blocking, rows, columns, wsz, msz, err) != 0) return -1;
+  const bool has_offsets = offsets && offsets_size > 0;
+
+  // Buffers may be larger than needed (reference :251-280 compares with "<").
+  if ((int64_t)quant_weights_size < wsz)
+    return fail(err, "Unexpected quantized weight tensor size: " +
+                         std::to_string(quant_weights_size) + " expected: " + std::to_string(wsz));
+  if ((int64_t)(quant_scales_size / sizeof(__half)) < msz)
+    return fail(err, "Unexpected scale tensor size: " +
+                         std::to_string(quant_scales_size / sizeof(__half)) +
+                         " expected: " + std::to_string(msz));
+  if (has_offsets && (int64_t)offsets_size < msz)
+    return fail(err, "Unexpected offset tensor size: " + std::to_string(offsets_size) +
+                         " expected: " + std::to_string(msz));
+  if (leadingDimension < rows)
+    return fail(err, "Leading dimension " + std::to_string(leadingDimension) +
+                         " is smaller than rows: " + std::to_string(rows));
+  // The last column needs only `rows` elements; the reference asks for a full
+  // columns * leadingDimension and so does this.
+  if ((int64_t)(weights_size / sizeof(__half)) < (int64_t)columns * leadingDimension)
+    return fail(err, "Unexpected weight tensor size: " +
+                         std::to_string(weights_size / sizeof(__half)) + " expected: " +
+                         std::to_string((int64_t)columns * leadingDimension));
+  if (!weights || !quant_weights || !quant_scales)
+    return fail(err, "Null tensor pointer");
+  if (reinterpret_cast<uintptr_t>(quant_weights) % 16 != 0)
+    return fail(err, "Quantized weight buffer must be 16-byte aligned");
+
+  const std::string e = blkq4::launch_quant_prepack(
+      block_size, column_wise_blocking, rows, columns, leadingDimension,
+      reinterpret_cast<cudaStream_t>(stream_ptr), reinterpret_cast<const __half*>(weights),
+      reinterpret_cast<uint8_t*>(quant_weights), reinterpret_cast<__half*>(quant_scales),
+      has_offsets ? reinterpret_cast<uint8_t*>(offsets) : nullptr);
+  if (!e.empty()) return fail(err, e);
+  return 0;
+}
+
+extern "C" int blkq4_fp16_gemm_sm80(int block_size, bool column_wise_blocking, int m, int n, int k,
+                                    void* stream_ptr, void const* act_ptr, size_t a_size,
+                                    void const* weights_ptr, size_t weights_size,
+                                    void const* scales_ptr, size_t scales_size,
+                                    void const* offsets_ptr, size_t offsets_size, void* output_ptr,
+                                    size_t output_size, void* err) {
+  if (!blkq4::supported_block(block_size))
+    return fail(err, "Unsupported block size: " + std::to_string(block_size));
+  if (m <= 0 || n <= 0 || k <= 0)
+    return fail(err, "Empty problem size: " + std::to_string(m) + "x" + std::to_string(n) + "x" +
+                         std::to_string(k));
+  const blkq4::Blocking b(block_size, column_wise_blocking);
+  // Reference kernel-level constraints (cutlass_ext/q4gemm/kernel/quantb_gemm.h:205-252):
+  // K % 64 == 0, whole quantization blocks, 16-byte aligned rows of A, W and the output.
+  if ((k % 64) != 0 || (k % b.bk) != 0 || (n % 16) != 0 || (n % b.bn) != 0)
+    return fail(err, "Kernel execution failed: Error Misaligned Operand or Invalid Problem: " +
+                         std::to_string(m) + "x" + std::to_string(n) + "x" + std::to_string(k));
+
+  const size_t meta = (size_t)(k / b.bk) * (size_t)(n / b.bn);
+  const size_t a_expect = (size_t)m * k * sizeof(__half);
+  if (a_size != a_expect)
+    return fail(err, "Unexpected activation tensor size: " + std::to_string(a_size) +
+                         " expected: " + std::to_string(a_expect));
+  const size_t w_expect = (size_t)(k / 2) * (size_t)(n / 2) * 2;
+  if (weights_size != w_expect)
+    return fail(err, "Unexpected weight tensor size: " + std::to_string(weights_size) +
+                         " expected: " + std::to_string(w_expect));
+  if (scales_size != meta * sizeof(__half))
+    return fail(err, "Unexpected scale tensor size: " + std::to_string(scales_size) +
+                         " expected: " + std::to_string(meta * sizeof(__half)));
+  const size_t o_expect = (size_t)m * n * sizeof(__half);
+  if (output_size != o_expect)
+    return fail(err, "Unexpected output tensor size: " + std::to_string(output_size) +
+                         " expected: " + std::to_string(o_expect));
+  const bool has_offsets = offsets_ptr && offsets_size > 0;
+  if (has_offsets && offsets_size != meta)
+    return fail(err, "Unexpected offsets tensor size: " + std::to_string(offsets_size) +
+                         " expected: " + std::to_string(meta));
+  if (!act_ptr || !weights_ptr || !scales_ptr || !output_ptr)
+    return fail(err, "Null tensor pointer");
+  if (reinterpret_cast<uintptr_t>(act_ptr) % 16 != 0 ||
+      reinterpret_cast<uintptr_t>(weights_ptr) % 16 != 0 ||
+      reinterpret_cast<uintptr_t>(output_ptr) % 16 != 0 ||
+      reinterpret_cast<uintptr_t>(scales_ptr) % 2 != 0)
+    return fail(err, "Kernel execution failed: Error Misaligned Operand");
+
+  auto stream = reinterpret_cast<cudaStream_t>(stream_ptr);
+  auto a = reinterpret_cast<const __half*>(act_ptr);
+  auto w = reinterpret_cast<const uint8_t*>(weights_ptr);
+  auto s = reinterpret_cast<const __half*>(scales_ptr);
+  auto z = has_offsets ? reinterpret_cast<const uint8_t*>(offsets_ptr) : nullptr;
+  auto o = reinterpret_cast<__half*>(output_ptr);
+
+  // m > 16 is the reference's own threshold between its two tile configurations
+  // (src/blkq4_f16_gemm_sm80.cu:343); here it separates the HBM-bound skinny
+  // kernel from the tcgen05 tensor-core kernel.
+  const std::string e =
+      (m <= 16) ? blkq4::launch_gemv(block_size, column_wise_blocking, m, n, k, stream, a, w, s, z, o)
+                : blkq4::launch_gemm_tc(block_size, column_wise_blocking, m, n, k, stream, a, w, s, z, o);
+  if (!e.empty()) return fail(err, "Kernel execution failed: " + e);
+  return 0;
+}
+
+extern "C" void* blkq4_errmsg_create(void) { return new std::string(); }
+extern "C" char const* blkq4_errmsg_cstr(void* p) {
+  return p ? reinterpret_cast<std::string*>(p)->c_str() : "";
+}
+extern "C" void blkq4_errmsg_destroy(void* p) { delete reinterpret_cast<std::string*>(p); }
+extern "C" char const* blkq4_version(void) { return "gemmlib_b200 0.1 sm_100a"; }

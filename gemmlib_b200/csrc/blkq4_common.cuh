@@ -1,0 +1,79 @@
+// Shared definitions of the blockwise-int4 (W4A16) kernels for sm_100a.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+namespace blkq4 {
+
+// Quantization block extents along K and N for a (block, orientation) pair:
+// column-wise blocks are (block x 1), row-wise blocks are (1 x block).
+// Reference: src/mickey/blk_q4/f16_quant_sm80.cuh:159-162.
+struct Blocking {
+  int bk, bn;
+  __host__ __device__ Blocking(int block, bool colwise)
+      : bk(colwise ? block : 1), bn(colwise ? 1 : block) {}
+};
+
+inline bool supported_block(int b) { return b == 16 || b == 32 || b == 64 || b == 128; }
+
+// Host-side launchers; each returns an empty string or an error text.
+std::string launch_quant_prepack(int block, bool colwise, int K, int N, int ld,
+                                 cudaStream_t stream, const __half* w, uint8_t* packed,
+                                 __half* scales, uint8_t* zp);
+
+std::string launch_gemv(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
+                        const __half* a, const uint8_t* packed, const __half* scales,
+                        const uint8_t* zp, __half* out);
+
+std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
+                           const __half* a, const uint8_t* packed, const __half* scales,
+                           const uint8_t* zp, __half* out);
+
+#ifdef __CUDACC__
+
+// One 32-bit word of the packed weight (4 bytes along kp at a fixed packed
+// column np) holds 8 nibbles:  q[2r,n0] q[2r+8,n0] q[2r,n0+8] q[2r+8,n0+8]
+// q[2r+1,n0] q[2r+9,n0] q[2r+1,n0+8] q[2r+9,n0+8]  (r = word index in its
+// 16-byte group, n0 = 16*(np/8) + np%8).  This turns it into four half2 of
+// fp16(16 + q), paired along k:
+//   h[0] = (n0;   2r, 2r+1)    h[1] = (n0;   2r+8, 2r+9)
+//   h[2] = (n0+8; 2r, 2r+1)    h[3] = (n0+8; 2r+8, 2r+9)
+// 0x4c00 is fp16 16.0, whose mantissa step is 1/64, so a nibble placed at bits
+// 6..9 adds its integer value.  Same numerics as the reference's weights2Half
+// (src/mickey/cutlass_ext/q4gemm/warp/quantb_meta_mma_tensor_op_tile_iterator.h:69-104).
+__device__ __forceinline__ void word_to_half16plus(uint32_t x, uint32_t h[4]) {
+  constexpr uint32_t kMask = 0x03c003c0u, kSixteen = 0x4c004c00u;
+  h[0] = ((x << 6) & kMask) | kSixteen;
+  h[1] = ((x << 2) & kMask) | kSixteen;
+  h[2] = ((x >> 2) & kMask) | kSixteen;
+  h[3] = ((x >> 6) & kMask) | kSixteen;
+}
+
+__device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t pack_half2(__half lo, __half hi) {
+  return (uint32_t)__half_as_ushort(lo) | ((uint32_t)__half_as_ushort(hi) << 16);
+}
+
+// Dequantization offset term rn_f16(scale * fp16(-16 - zp)); the dequantized
+// weight is then fma_rn_f16(scale, fp16(16 + q), offset).  Two fp16 roundings,
+// as in the reference kernel (same file as above, :436-543).
+__device__ __forceinline__ __half dequant_offset(__half scale, int zp) {
+  return __hmul_rn(scale, __int2half_rn(-16 - zp));
+}
+
+#endif  // __CUDACC__
+
+}  // namespace blkq4

@@ -1,0 +1,120 @@
+/*
+ * C ABI of the blockwise-int4 weight-only GEMM library, B200 (sm_100a) build.
+ *
+ * The first three entry points are the drop-in boundary: they keep the names,
+ * argument order, argument meaning, return convention and data-layout contract
+ * of the reference library's public header (reference include/ms_blkq4gemm.h:
+ * blkq4_fp16_gemm_sm80 :41-50, blkq4_fp16_quant_sm80 :71-80,
+ * blkq4_fp16_quant_size_sm80 :94-100), so a caller linked against the reference
+ * links against this library unchanged.  The `_sm80` suffix is kept for that
+ * reason only; the kernels behind it are written for sm_100a and there is no
+ * other code path (no CPU fallback: without a usable device the calls fail).
+ *
+ * Like the reference header this file includes nothing: have <cstdint> and
+ * <cstddef> included first.  The signatures use `bool` and a reference
+ * parameter, so the header is C++.
+ *
+ * Conventions shared by all entry points
+ *   - return 0 on success, -1 on error.  `error_message` is a `std::string*`
+ *     passed as `void*` (may be null); it is written only on error.
+ *   - every `*_ptr` is a device pointer owned by the caller, on the current
+ *     device.  `stream` is a `cudaStream_t` passed as `void*` (null = default
+ *     stream).  Work is enqueued on `stream`; the calls do not synchronise and
+ *     allocate no device memory.
+ *   - every `*_size` argument is a size in BYTES.
+ *
+ * Layout contract (identical to the reference)
+ *   weights       fp16, K x N column-major with leading dimension >= K; this is
+ *                 a PyTorch Linear.weight [out_features, in_features] as is.
+ *   block         16, 32 or 64 (128 is accepted as an extension).  Column-wise
+ *                 blocking: `block` consecutive k of one column share a scale.
+ *                 Row-wise: `block` consecutive n of one row share a scale.
+ *   quant weights K * N / 2 bytes, column-major [K, N/2].  Byte (kp, np) holds
+ *                 q[k, n] in the low and q[k + 8, n] in the high nibble, with
+ *                 n = 16*(np/8) + np%8 + 8*(kp%4 & 1) and
+ *                 k = 16*(kp/16) + 2*((kp%16)/4) + (kp%4 >> 1).
+ *   scales        fp16, (K/bk) * (N/bn) entries.  Column-wise: row-major
+ *                 [K/block, N].  Row-wise: column-major [K, N/block] with every
+ *                 16 rows permuted to 0 1 8 9 2 3 10 11 4 5 12 13 6 7 14 15.
+ *   zero points   one 4-bit value per uint8_t, same shape as scales.  Row-wise:
+ *                 every 16 rows permuted to 0 8 1 9 2 10 3 11 4 12 5 13 6 14 7 15.
+ *                 A null pointer or zero size means symmetric quantization
+ *                 (zero point 8; the scale may then be negative).
+ *   activations   fp16 row-major [M, K];  output fp16 row-major [M, N].
+ */
+
+#pragma once
+
+extern "C" {
+
+/**
+ * output[M,N] = act[M,K] x dequantize(weights[K,N]), fp32 accumulation, fp16 out.
+ * Replaces reference include/ms_blkq4gemm.h:41-50 (src/blkq4_f16_gemm_sm80.cu:319-429).
+ *
+ * Sizes must match exactly: a_size = 2*M*K, weights_size = K*N/2,
+ * scales_size = 2*meta, offsets_size = meta (or 0), output_size = 2*M*N, with
+ * meta = (K/bk)*(N/bn).  Requires M, N, K > 0, K % 64 == 0, N % 16 == 0 and
+ * whole quantization blocks.  M <= 16 takes the memory-bound skinny kernel,
+ * larger M the tensor-core kernel.
+ */
+int blkq4_fp16_gemm_sm80(
+  int block_size,
+  bool column_wise_blocking,
+  int m, int n, int k, void* stream,
+  void const* act_ptr, size_t a_size,
+  void const* weights_ptr, size_t weights_size,
+  void const* scales_ptr, size_t scales_size,
+  void const* offsets_ptr, size_t offsets_size,
+  void* output_ptr, size_t output_size,
+  void* error_message);
+
+/**
+ * Quantize an fp16 weight matrix blockwise to 4 bits and write it, its scales and
+ * (optionally) its zero points in the prepacked layout the GEMM consumes.
+ * Replaces reference include/ms_blkq4gemm.h:71-80 (src/blkq4_f16_gemm_sm80.cu:465-531).
+ *
+ * rows = K (input features), columns = N (output features).  Buffer sizes may
+ * exceed what is needed (>=), as in the reference.  One fused kernel; unlike the
+ * reference no temporary device buffers are allocated.
+ */
+extern int blkq4_fp16_quant_sm80(
+    int block_size,
+    bool column_wise_blocking,
+    int rows, int columns, int leadingDimension,
+    void* stream,
+    void const* weights, size_t weights_size,
+    void* quant_weights, size_t quant_weights_size,
+    void* quant_scales, size_t quant_scales_size,
+    void* offsets, size_t offsets_size,
+    void* error_message);
+
+/**
+ * Element counts of the quantized tensors: quant_weights_size in uint8_t,
+ * quant_meta_size in meta entries (fp16 scales, uint8_t zero points).
+ * Replaces reference include/ms_blkq4gemm.h:94-100 (src/blkq4_f16_gemm_sm80.cu:431-463).
+ * Host only.  Rejects rows % 64 != 0, columns % 32 != 0, empty shapes,
+ * unsupported block sizes, and shapes whose last quantization block would be
+ * partial (the reference lets some of those through and then writes out of
+ * bounds; see the note in src of this library).
+ */
+int blkq4_fp16_quant_size_sm80(
+    int block_size,
+    bool column_wise_blocking,
+    int rows, int columns,
+    int64_t& quant_weights_size,
+    int64_t& quant_meta_size,
+    void* error_message);
+
+/*
+ * Additions with no counterpart in the reference.  The reference reports errors
+ * through a std::string*, which only a C++ caller can supply.  These three let
+ * a C, ctypes, cgo or JNI caller own such an object.
+ */
+void* blkq4_errmsg_create(void);              /* new std::string                 */
+char const* blkq4_errmsg_cstr(void* errmsg);  /* its c_str(); valid until reused */
+void blkq4_errmsg_destroy(void* errmsg);      /* delete                          */
+
+/** Library identification: "gemmlib_b200 <version> sm_100a". */
+char const* blkq4_version(void);
+
+}  // extern "C"

@@ -1,0 +1,141 @@
+"""GPU parity of the W4A16 GEMM / GEMV kernels, through the C ABI.
+
+Two bars.  (1) On the reference tests' known-answer family every product and
+partial sum is exact, and the result must EQUAL the naive fp32-accumulate GEMM on
+the host-dequantized weights (the reference's TensorEquals criterion).  (2) On
+Gaussian inputs: max |delta| <= 1e-2 * sqrt(K) * max|a| * max|w| against the oracle's
+dequantize-then-GEMM (fp32 accumulate), plus a much tighter relative check that
+catches layout mistakes the loose bound would hide."""
+import numpy as np
+import pytest
+
+from oracle import blkq4_oracle as O
+from tests._util import REF_GEMM_CASES, bits, gaussian_act, gaussian_weight
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+def to_cuda(a):
+    return None if a is None else torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def gpu_gemm(block, colwise, a_mk, N, packed, scales, zp):
+    from gemmlib_b200 import capi
+
+    M, K = a_mk.shape
+    a, pw, ps, pz = to_cuda(a_mk), to_cuda(packed), to_cuda(scales), to_cuda(zp)
+    out = torch.full((M, N), float("nan"), dtype=torch.float16, device="cuda")
+    capi.gemm(block, colwise, M, N, K, a, pw, ps, pz, out)
+    torch.cuda.synchronize()
+    return out.cpu().numpy()
+
+
+def kat_problem(block, colwise, has_zp, M, N, K):
+    q, s, z = O.kat_generate(block, colwise, K, N, has_zp)
+    pw = O.prepack_weights(K, N, q)
+    ps, pz = O.prepack_meta(block, colwise, K, N, s, z)
+    a = O.kat_activations(M, K)
+    return a, pw, ps, pz
+
+
+@pytest.mark.parametrize("case", REF_GEMM_CASES, ids=lambda c: "-".join(map(str, c)))
+def test_reference_gemm_cases_exact(case):
+    """The reference's BlkQ4Fp16Gemm.Sm80Test list (test/blkq4_fp16_gemm_sm80_test.cu:480-518)."""
+    block, colwise, has_zp, M, N, K = case
+    a, pw, ps, pz = kat_problem(block, colwise, has_zp, M, N, K)
+    want = O.dequant_gemm(block, colwise, a, N, pw, ps, pz)
+    got = gpu_gemm(block, colwise, a, N, pw, ps, pz)
+    assert (bits(got) == bits(want)).all(), f"{(bits(got) != bits(want)).sum()} of {got.size} differ"
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 7, 8, 9, 15, 16, 17, 33, 64, 100, 128, 129, 255, 256, 300])
+def test_every_m_class_exact(M):
+    """Row counts around the kernel boundaries (skinny <= 8, <= 16, tensor-core tiles),
+    block 128 included, on exact known-answer data."""
+    for block, colwise, has_zp, N, K in [(64, True, True, 352, 256), (128, True, False, 256, 384),
+                                         (32, False, True, 96, 192), (16, True, False, 2080, 64)]:
+        a, pw, ps, pz = kat_problem(block, colwise, has_zp, M, N, K)
+        want = O.dequant_gemm(block, colwise, a, N, pw, ps, pz)
+        got = gpu_gemm(block, colwise, a, N, pw, ps, pz)
+        assert (bits(got) == bits(want)).all(), (M, block, colwise, has_zp, N, K)
+
+
+def check_gaussian(block, colwise, has_zp, M, N, K, sigma=0.02):
+    w = gaussian_weight(N, K, sigma=sigma, seed=K + N)
+    a = gaussian_act(M, K, seed=M).numpy()
+    pw, ps, pz = O.quant_prepack(block, colwise, w.numpy(), has_zp)
+    got = gpu_gemm(block, colwise, a, N, pw, ps, pz).astype(np.float64)
+    assert np.isfinite(got).all()
+    wdq = O.dequant(block, colwise, K, N, pw, ps, pz)
+    want = O.gemm(a, wdq).astype(np.float64)
+    tol = 1e-2 * np.sqrt(K) * np.abs(a.astype(np.float32)).max() * np.abs(wdq.astype(np.float32)).max()
+    err = np.abs(got - want).max()
+    assert err <= tol, (err, tol)
+    # Tight check against the kernel's own dequantization formula: what remains is
+    # fp32 summation order and one fp16 output rounding.
+    wk = O.dequant(block, colwise, K, N, pw, ps, pz, kernel_formula=True)
+    exact = a.astype(np.float64) @ wk.astype(np.float64).T
+    scale = np.sqrt(K) * a.astype(np.float64).std() * wk.astype(np.float64).std()
+    assert np.abs(got - exact).max() <= 4e-3 * scale + 2 ** -11 * np.abs(exact).max(), np.abs(got - exact).max()
+
+
+@pytest.mark.parametrize("colwise", [True, False])
+@pytest.mark.parametrize("has_zp", [True, False])
+@pytest.mark.parametrize("block", [16, 32, 64, 128])
+@pytest.mark.parametrize("M", [1, 5, 16, 48, 512])
+def test_gaussian_tolerance(block, colwise, has_zp, M):
+    check_gaussian(block, colwise, has_zp, M, 384, 512)
+
+
+def test_config_c1_cpu_reference_case():
+    """configs[0]: M16 K4096 N4096 b32 column-wise with zero points."""
+    check_gaussian(32, True, True, 16, 4096, 4096)
+
+
+def test_config_c2_decode_gemv():
+    """configs[1]: M1 K4096 N11008 b64 column-wise symmetric."""
+    check_gaussian(64, True, False, 1, 11008, 4096)
+
+
+def test_config_c3_prefill_gemm_rows_sample():
+    """configs[2]: M2048 K4096 N4096 b32 zp.  The oracle GEMM at full M is slow; the GPU
+    runs the full problem and 64 sampled rows are checked, together with linearity
+    in A (a size-independent property): f(2a) == 2 f(a) exactly in fp16."""
+    block, colwise, has_zp, M, N, K = 32, True, True, 2048, 4096, 4096
+    w = gaussian_weight(N, K, seed=0)
+    a = gaussian_act(M, K, seed=1).numpy()
+    pw, ps, pz = O.quant_prepack(block, colwise, w.numpy(), has_zp)
+    got = gpu_gemm(block, colwise, a, N, pw, ps, pz)
+    rows = np.random.default_rng(0).choice(M, 64, replace=False)
+    wdq = O.dequant(block, colwise, K, N, pw, ps, pz)
+    want = O.gemm(a[rows], wdq).astype(np.float64)
+    tol = 1e-2 * np.sqrt(K) * np.abs(a.astype(np.float32)).max() * np.abs(wdq.astype(np.float32)).max()
+    assert np.abs(got[rows].astype(np.float64) - want).max() <= tol
+    assert np.abs(got[rows].astype(np.float64) - want).max() <= 0.02  # outputs are O(1)
+    got2 = gpu_gemm(block, colwise, (a * np.float16(2)).astype(np.float16), N, pw, ps, pz)
+    assert (bits(got2) == bits((got * np.float16(2)).astype(np.float16))).all()
+
+
+def test_config_c4_sweep_shape_block128():
+    """configs[3] shapes (K8192 N28672 b128 symmetric), one shard of 8 (N=3584)."""
+    for M in (1, 4, 16, 64, 256):
+        check_gaussian(128, True, False, M, 3584, 8192, sigma=0.015)
+
+
+def test_output_canaries_untouched():
+    """The kernels write exactly M*N outputs: guard bytes around the buffer survive."""
+    from gemmlib_b200 import capi
+
+    for M in (1, 16, 40):
+        block, colwise, N, K = 32, True, 96, 128
+        a, pw, ps, pz = kat_problem(block, colwise, True, M, N, K)
+        buf = torch.full((M * N + 512,), 7.0, dtype=torch.float16, device="cuda")
+        out = buf[256 : 256 + M * N]
+        capi.gemm(block, colwise, M, N, K, to_cuda(a), to_cuda(pw), to_cuda(ps), to_cuda(pz), out)
+        torch.cuda.synchronize()
+        h = buf.cpu().numpy()
+        assert (h[:256] == 7).all() and (h[256 + M * N :] == 7).all()
+        want = O.dequant_gemm(block, colwise, a, N, pw, ps, pz)
+        assert (bits(h[256 : 256 + M * N].reshape(M, N)) == bits(want)).all()
