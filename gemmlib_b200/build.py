@@ -69,7 +69,7 @@ def build_lib(verbose: bool = False, force: bool = False) -> str:
                 if verbose and log:
                     print(log, file=sys.stderr)
     if jobs or not os.path.exists(LIB) or os.path.getmtime(LIB) < _newest(objs):
-        run([nvcc, "-shared", "-o", LIB, *objs, "-lcudart", "-lcuda"])
+        run([nvcc, "-shared", "-o", LIB, *objs, "-lcudart"])
     return LIB
 
 

@@ -21,6 +21,7 @@ SYMBOLS = (
     "blkq4_errmsg_create",
     "blkq4_errmsg_cstr",
     "blkq4_errmsg_destroy",
+    "blkq4_last_kernel_status",
     "blkq4_version",
 )
 
@@ -49,6 +50,8 @@ def _load() -> ctypes.CDLL:
     lib.blkq4_errmsg_cstr.restype = ctypes.c_char_p
     lib.blkq4_errmsg_destroy.argtypes = [vp]
     lib.blkq4_version.restype = ctypes.c_char_p
+    lib.blkq4_last_kernel_status.argtypes = [vp]
+    lib.blkq4_last_kernel_status.restype = i
     return lib
 
 
@@ -79,6 +82,11 @@ def _ptr_size(t):
 
 def version() -> str:
     return lib.blkq4_version().decode()
+
+
+def last_kernel_status(stream=0) -> int:
+    """Synchronise ``stream`` and return the tensor-core kernel's device status word."""
+    return int(lib.blkq4_last_kernel_status(stream))
 
 
 def quant_size(block_size: int, column_wise: bool, rows: int, columns: int):

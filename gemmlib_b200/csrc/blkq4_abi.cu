@@ -161,4 +161,7 @@ extern "C" char const* blkq4_errmsg_cstr(void* p) {
   return p ? reinterpret_cast<std::string*>(p)->c_str() : "";
 }
 extern "C" void blkq4_errmsg_destroy(void* p) { delete reinterpret_cast<std::string*>(p); }
+extern "C" int blkq4_last_kernel_status(void* stream_ptr) {
+  return blkq4::read_gemm_tc_error(reinterpret_cast<cudaStream_t>(stream_ptr));
+}
 extern "C" char const* blkq4_version(void) { return "gemmlib_b200 0.1 sm_100a"; }

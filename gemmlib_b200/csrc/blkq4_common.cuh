@@ -33,6 +33,10 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
                            const __half* a, const uint8_t* packed, const __half* scales,
                            const uint8_t* zp, __half* out);
 
+// Synchronises `stream` and returns the tensor-core kernel's device error word
+// (0 = every bounded wait completed; -1 = the stream itself reported an error).
+int read_gemm_tc_error(cudaStream_t stream);
+
 #ifdef __CUDACC__
 
 // One 32-bit word of the packed weight (4 bytes along kp at a fixed packed

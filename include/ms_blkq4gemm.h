@@ -114,6 +114,15 @@ void* blkq4_errmsg_create(void);              /* new std::string                
 char const* blkq4_errmsg_cstr(void* errmsg);  /* its c_str(); valid until reused */
 void blkq4_errmsg_destroy(void* errmsg);      /* delete                          */
 
+/**
+ * Synchronises `stream` and returns the device-side status word of the tensor-core
+ * kernel: 0 when every in-kernel wait completed.  Its waits on mbarriers are bounded;
+ * one that expires makes the CTA drain and records (role << 8 | barrier) here instead
+ * of hanging the GPU.  -1 if the stream itself is in error.  No counterpart in the
+ * reference, whose kernels have no such waits.
+ */
+int blkq4_last_kernel_status(void* stream);
+
 /** Library identification: "gemmlib_b200 <version> sm_100a". */
 char const* blkq4_version(void);
 

@@ -102,7 +102,8 @@ def test_config_c2_decode_gemv():
 def test_config_c3_prefill_gemm_rows_sample():
     """configs[2]: M2048 K4096 N4096 b32 zp.  The oracle GEMM at full M is slow; the GPU
     runs the full problem and 64 sampled rows are checked, together with linearity
-    in A (a size-independent property): f(2a) == 2 f(a) exactly in fp16."""
+    in A (a size-independent property): f(2a) == 2 f(a) exactly in fp16
+    (outside the subnormal range)."""
     block, colwise, has_zp, M, N, K = 32, True, True, 2048, 4096, 4096
     w = gaussian_weight(N, K, seed=0)
     a = gaussian_act(M, K, seed=1).numpy()
@@ -115,7 +116,10 @@ def test_config_c3_prefill_gemm_rows_sample():
     assert np.abs(got[rows].astype(np.float64) - want).max() <= tol
     assert np.abs(got[rows].astype(np.float64) - want).max() <= 0.02  # outputs are O(1)
     got2 = gpu_gemm(block, colwise, (a * np.float16(2)).astype(np.float16), N, pw, ps, pz)
-    assert (bits(got2) == bits((got * np.float16(2)).astype(np.float16))).all()
+    # doubling is exact except where the fp16 result is subnormal
+    normal = np.abs(got.astype(np.float32)) >= 2.0 ** -13
+    assert (bits(got2)[normal] == bits((got * np.float16(2)).astype(np.float16))[normal]).all()
+    assert np.abs(got2.astype(np.float32) - 2 * got.astype(np.float32))[~normal].max(initial=0) <= 2.0 ** -23
 
 
 def test_config_c4_sweep_shape_block128():

@@ -45,7 +45,10 @@ def assert_same(got, want, what=""):
 def test_known_answer_round_trip(block, colwise, has_zp):
     """The reference's testPrepack: dequantize known nibbles/scales/zps on the host,
     quantize on the device, expect the prepacked originals back exactly."""
-    shapes = REF_PREPACK_SHAPES + [(576, 672), (960, 2080)] if block <= 32 else [(128, 128), (576, 1024), (256, 384)]
+    # (960, 2080) is a reference GEMM-test shape, used there row-wise only: column-wise its
+    # generator's int arithmetic overflows (c * v with v > 5e6) and the identity is lost.
+    shapes = (REF_PREPACK_SHAPES + [(576, 672)] + ([] if colwise else [(960, 2080)])) if block <= 32 \
+        else [(128, 128), (576, 1024), (256, 384)]
     for K, N in shapes:
         try:
             O.quant_size(block, colwise, K, N)
