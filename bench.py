@@ -1,0 +1,405 @@
+#!/usr/bin/env python
+"""Benchmark of the W4A16 hot path on B200.  Prints ONE JSON line (rank 0).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (N = 1): the decode GEMV the headline metric is quoted on,
+M=1, K=4096, N=11008, block 64 column-wise symmetric, fp16 scales; weights
+~N(0, 0.02), activations ~N(0, 1), torch CPU generator, seed 0 (+ layer index).
+One layer's 24 MB would sit in the 126 MB L2, so a STEP is one pass over 16 such
+layers with distinct weights (384 MB > L2): 16 launches of the skinny kernel.
+`value` = algorithmic bytes of all launches / device time, inputs resident in HBM,
+launches replayed from a CUDA graph.  `e2e` = the same pass through the public
+`BlkQ4Linear.forward` with the activation copied from pinned host memory and the
+result copied back, every layer, inside the timed region.
+
+With N > 1 (torchrun, one rank per GPU) the layer is N-sharded: each rank owns a
+c2-sized shard of a layer g times as wide, and every layer ends with the all-gather
+of the outputs (NCCL); per-GPU work is fixed, so "scaling" is "weak".
+
+`--impl reference` times the reference's CPU-side path for the same workload
+(dequantize the packed weight, then GEMM with fp32 accumulation: the oracle's C
+restatement, OpenMP over all host threads) on a bounded sample.
+
+Also reported, as extra keys: the prefill GEMM (M=2048 K=4096 N=4096, block 32 with
+zero points) in TFLOP/s against the tensor roofline, and quantize+prepack in GB/s.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+C2 = dict(M=1, K=4096, N=11008, block=64, col_wise=True, has_zp=False, sigma=0.02)
+C3 = dict(M=2048, K=4096, N=4096, block=32, col_wise=True, has_zp=True, sigma=0.02)
+LAYERS = 16  # distinct weight sets per step: 16 x 24 MB > 126 MB of L2
+
+
+def algorithmic_bytes(M, K, N, block, col_wise, has_zp):
+    """bytes = K*N/2 (packed W) + 2*meta (scales) + [meta] (zero points) + 2*M*K + 2*M*N."""
+    bk, bn = (block, 1) if col_wise else (1, block)
+    meta = (K // bk) * (N // bn)
+    return K * N // 2 + 2 * meta + (meta if has_zp else 0) + 2 * M * K + 2 * M * N
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return dict(hbm_gbs=d["hbm_gbs"], tflops=d["bf16_tflops"], tflops_sustained=d.get("bf16_tflops_sustained"),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, tflops=1590.0, tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples while a region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.gpu)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, t0, t1):
+        rows = [r for (t, r) in self.rows if t0 <= t <= t1 and len(r) >= 9]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm = [float(r[1]) for r in rows]
+        reasons = set()
+        for r in rows:
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": float(rows[0][2]), "reasons": sorted(reasons),
+                "power_w_max": max(float(r[3]) for r in rows), "samples": len(rows)}
+
+
+# ------------------------------------------------------------------------------------------
+# reference arm: the reference's CPU-side path (dequantize, then GEMM), oracle port
+
+
+def cpu_dequant_gemm_sample(cfg, min_seconds=10.0, max_seconds=25.0):
+    """Time oracle dequantize + GEMM (all host threads) on the c2 workload; returns
+    (GB/s of algorithmic bytes, seconds per pass, passes, threads)."""
+    import numpy as np
+    import torch
+
+    from oracle import blkq4_oracle as O
+
+    g = torch.Generator().manual_seed(0)
+    w = (torch.randn(cfg["N"], cfg["K"], generator=g) * cfg["sigma"]).to(torch.float16).numpy()
+    a = torch.randn(cfg["M"], cfg["K"], generator=g).to(torch.float16).numpy()
+    pw, ps, pz = O.quant_prepack(cfg["block"], cfg["col_wise"], w, cfg["has_zp"])
+    O.dequant_gemm(cfg["block"], cfg["col_wise"], a, cfg["N"], pw, ps, pz)  # warm
+    times = []
+    t_start = time.time()
+    while True:
+        t = time.perf_counter()
+        O.dequant_gemm(cfg["block"], cfg["col_wise"], a, cfg["N"], pw, ps, pz)
+        times.append(time.perf_counter() - t)
+        el = time.time() - t_start
+        if (el >= min_seconds and len(times) >= 3) or el >= max_seconds:
+            break
+    sec = statistics.median(times)
+    nbytes = algorithmic_bytes(cfg["M"], cfg["K"], cfg["N"], cfg["block"], cfg["col_wise"], cfg["has_zp"])
+    return nbytes / sec / 1e9, sec, len(times), O.num_threads()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    gbs_runs = []
+    t_all = time.time()
+    for _ in range(max(1, min(args.steps, 3))):
+        gbs, sec, passes, threads = cpu_dequant_gemm_sample(C2, min_seconds=3.0, max_seconds=8.0)
+        gbs_runs.append(gbs)
+    gbs = statistics.median(gbs_runs)
+    nbytes = algorithmic_bytes(**{k: C2[k] for k in ("M", "K", "N", "block", "col_wise", "has_zp")})
+    line = {
+        "impl": "reference",
+        "metric": "W4A16 effective HBM GB/s (M<=16)", "value": round(gbs, 3), "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(LAYERS * nbytes / gbs / 1e6, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": f"one c2 layer (dequantize 4096x11008 + GEMV M=1), median of repeated passes, "
+                                   f"{time.time() - t_all:.0f} s of CPU time; the reference ships no CPU GEMM, "
+                                   "this is the oracle's restatement of its test-side dequantize-then-GEMM"},
+        "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def workload_config(n_gpus):
+    return {
+        "workload": "c2 decode GEMV: M=1 K=4096 N=11008 block=64 column-wise symmetric, fp16 scales"
+                    + (f"; N-sharded x{n_gpus}: each rank owns one c2-sized shard, all-gather of outputs per layer"
+                       if n_gpus > 1 else ""),
+        "launches_per_step": LAYERS,
+        "l2": f"inputs larger than L2: a step walks {LAYERS} layers with distinct weights ({LAYERS} x 24 MB > 126 MB)",
+        "parallelism": f"n-shard{n_gpus}" if n_gpus > 1 else "single",
+    }
+
+
+# ------------------------------------------------------------------------------------------
+# our arm
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from gemmlib_b200 import capi
+    from gemmlib_b200.ms_blkq4linear import BlkQ4Linear
+    from gemmlib_b200.sharded import gather_columns
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the measured path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = measured_peaks()
+    cfg = C2
+    M, K, N = cfg["M"], cfg["K"], cfg["N"]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- build the layers (quantize + prepack on the device, timed for the extra line) ----
+    layers, quant_ms = [], []
+    for i in range(LAYERS):
+        g = torch.Generator().manual_seed(i + 1000 * rank)
+        w = (torch.randn(N, K, generator=g) * cfg["sigma"]).to(torch.float16).to(dev)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        layers.append(BlkQ4Linear(cfg["block"], cfg["col_wise"], not cfg["has_zp"], w))
+        e1.record()
+        torch.cuda.synchronize()
+        quant_ms.append(e0.elapsed_time(e1))
+        del w
+    g = torch.Generator().manual_seed(0)
+    a_host = torch.randn(M, K, generator=g).to(torch.float16).pin_memory()
+    a_dev = a_host.to(dev)
+    outs = [torch.empty(M, N, dtype=torch.float16, device=dev) for _ in range(LAYERS)]
+    full = None
+
+    def step_resident():
+        nonlocal full
+        for lyr, o in zip(layers, outs):
+            lyr(a_dev, out=o)
+            if world > 1:
+                full = gather_columns(o)
+
+    # ---- CUDA graph of one step ----
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            step_resident()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        step_resident()
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        graph.replay()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_wall0 = time.time()
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    barrier()
+    t_wall1 = time.time()
+    ms = e0.elapsed_time(e1)
+    # keep the same work running for >= 1.5 s so that the 100 ms clock sampler sees it under load
+    t_ext0 = time.time()
+    while time.time() - t_ext0 < 1.5:
+        for _ in range(200):
+            graph.replay()
+        torch.cuda.synchronize()
+    t_ext1 = time.time()
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    status = capi.last_kernel_status()
+
+    nbytes = algorithmic_bytes(M, K, N, cfg["block"], cfg["col_wise"], cfg["has_zp"])
+    total_bytes = nbytes * LAYERS * args.steps * world
+    value = total_bytes / (ms * 1e-3) / 1e9
+    launch_us = ms * 1e3 / (args.steps * LAYERS)
+
+    # ---- end to end through BlkQ4Linear.forward with host buffers ----
+    out_host = torch.empty(M, N * world, dtype=torch.float16).pin_memory()
+
+    def step_e2e():
+        for lyr in layers:
+            x = a_host.to(dev, non_blocking=True)
+            y = lyr(x)
+            if world > 1:
+                y = gather_columns(y)
+            out_host.copy_(y, non_blocking=True)
+
+    for _ in range(3):
+        step_e2e()
+    barrier()
+    e2e_steps = min(args.steps, 200)
+    e0.record()
+    for _ in range(e2e_steps):
+        step_e2e()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = nbytes * LAYERS * e2e_steps * world / (e2e_ms * 1e-3) / 1e9
+
+    line = {
+        "metric": "W4A16 effective HBM GB/s (M<=16)", "value": round(value, 2), "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": round(ms / args.steps, 5), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": workload_config(world),
+        "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": LAYERS * M * K * 2,
+                "d2h_bytes_per_step": LAYERS * M * N * world * 2, "steps": e2e_steps,
+                "api": "BlkQ4Linear.forward, pinned host activation in, pinned host result out, per layer"},
+        "gpu_launches": args.steps * LAYERS,
+        "kernel_status": status,
+    }
+    if rank == 0:
+        sampler_summary = None
+        time.sleep(0.15)
+        sampler.stop()
+        timed = sampler.summary(t_wall0, t_wall1)
+        ext = sampler.summary(t_ext0, t_ext1)
+        sampler_summary = timed if timed["samples"] >= 3 else dict(ext, note="timed region shorter than the sampler "
+                                                                   "period; sampled while replaying the same graph right after it")
+        line["clocks"] = sampler_summary
+        line["roofline"] = {
+            "bound": "hbm", "achieved": round(nbytes / (launch_us * 1e-6) / 1e9, 2), "peak": peaks["hbm_gbs"],
+            "unit": "GB/s", "frac": round(nbytes / (launch_us * 1e-6) / 1e9 / peaks["hbm_gbs"], 4),
+            "traffic": TRAFFIC_BYTES_PER_LAUNCH, "kernel": "gemv_kernel<1,1,4,true>",
+            "bytes_per_launch": nbytes, "us_per_launch": round(launch_us, 3), "peak_source": peaks["source"],
+        }
+    if world == 1:
+        line["quant_prepack"] = {
+            "GB/s": round((2 * K * N + K * N // 2 + 2 * (K // cfg["block"]) * N) / (statistics.median(quant_ms) * 1e-3) / 1e9, 1),
+            "ms_per_layer": round(statistics.median(quant_ms), 4),
+            "note": "single calls through BlkQ4Linear.__init__ (includes allocation), c2 layer"}
+        line["gemm"] = bench_gemm_c3(torch, dev, peaks)
+        gbs, sec, passes, threads = cpu_dequant_gemm_sample(cfg)
+        line["cpu_baseline"] = {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port",
+                                "sample": f"one c2 layer, {passes} passes of oracle dequantize+GEMV, median {sec * 1e3:.1f} ms per pass"}
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the timed kernel, from the
+# committed ncu capture (profiles/); None until a capture exists.
+TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def bench_gemm_c3(torch, dev, peaks):
+    """Prefill GEMM (configs[2]) through BlkQ4Linear.forward: TFLOP/s against the tensor roofline."""
+    from gemmlib_b200.ms_blkq4linear import BlkQ4Linear
+
+    c = C3
+    sets = 4  # 4 x (8 MB W + 16 MB A + 16 MB out) > L2
+    layers, acts, outs = [], [], []
+    for i in range(sets):
+        g = torch.Generator().manual_seed(100 + i)
+        w = (torch.randn(c["N"], c["K"], generator=g) * c["sigma"]).to(torch.float16).to(dev)
+        layers.append(BlkQ4Linear(c["block"], c["col_wise"], not c["has_zp"], w))
+        acts.append(torch.randn(c["M"], c["K"], generator=g).to(torch.float16).to(dev))
+        outs.append(torch.empty(c["M"], c["N"], dtype=torch.float16, device=dev))
+    for _ in range(3):
+        for lyr, x, o in zip(layers, acts, outs):
+            lyr(x, out=o)
+    torch.cuda.synchronize()
+    reps = 50
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        for lyr, x, o in zip(layers, acts, outs):
+            lyr(x, out=o)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (reps * sets)
+    flops = 2.0 * c["M"] * c["N"] * c["K"]
+    tf = flops / (us * 1e-6) / 1e12
+    return {"metric": "W4A16 TFLOP/s (M>=256)", "workload": "c3 prefill GEMM M=2048 K=4096 N=4096 block=32 zero points",
+            "value": round(tf, 1), "unit": "TFLOP/s", "us_per_call": round(us, 2),
+            "roofline": {"bound": "tensor", "achieved": round(tf, 1), "peak": peaks["tflops"], "unit": "TFLOP/s",
+                         "frac": round(tf / peaks["tflops"], 4), "peak_source": peaks["source"]},
+            "frac_of_nominal_2250": round(tf / 2250.0, 4)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=int(os.environ.get("WORLD_SIZE", "1")))
+    ap.add_argument("--steps", type=int, default=500)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -73,5 +73,44 @@ def build_lib(verbose: bool = False, force: bool = False) -> str:
     return LIB
 
 
+EXT_NAME = "ms_blkq4linear_ext"
+
+
+def ext_path():
+    import sysconfig
+
+    return os.path.join(PKG, EXT_NAME + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_ext(force: bool = False) -> str:
+    """Build the PyTorch extension ``ms_blkq4linear_ext`` next to the library it links."""
+    build_lib()
+    out = ext_path()
+    src = os.path.join(CSRC, "ms_blkq4linear_ext.cpp")
+    if not force and os.path.exists(out) and os.path.getmtime(out) >= max(os.path.getmtime(src), os.path.getmtime(LIB)):
+        return out
+    import sysconfig
+
+    import torch
+    from torch.utils import cpp_extension
+
+    inc = cpp_extension.include_paths("cuda")
+    tlib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-DTORCH_EXTENSION_NAME=" + EXT_NAME,
+           "-DTORCH_API_INCLUDE_EXTENSION_H", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+           "-I" + os.path.join(ROOT, "include"), "-I" + sysconfig.get_paths()["include"]]
+    cmd += ["-isystem" + p for p in inc]
+    cmd += [src, "-o", out, "-L" + PKG, "-l:libms_blkq4gemm.so", "-Wl,-rpath,$ORIGIN",
+            "-L" + tlib, "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python",
+            "-Wl,-rpath," + tlib]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("building ms_blkq4linear_ext failed:\n" + r.stdout + r.stderr)
+    return out
+
+
 if __name__ == "__main__":
     print(build_lib(verbose="-v" in sys.argv, force="-f" in sys.argv))
+    if "--ext" in sys.argv:
+        print(build_ext(force="-f" in sys.argv))
+

@@ -1,0 +1,72 @@
+"""``BlkQ4Linear``: blockwise-int4 weight-only linear layer.
+
+Mirror of the reference module python/ms_blkq4linear.py:10-28: same class name,
+constructor arguments ``(block_size, col_wise, scale_only, weights,
+bias_tensor=None)``, attributes and ``forward(input)``.  Quantization and prepack
+happen in the constructor (on the device the weights live on); ``forward`` runs the
+W4A16 GEMM/GEMV and adds the bias.
+
+Additive differences: the packed tensors are registered as buffers, so they travel
+with ``state_dict()`` / ``.to()``; the constructor's diagnostic prints are gone;
+``from_packed`` rebuilds a layer from already-quantized tensors; inputs with leading
+batch dimensions are flattened to 2-D and restored.
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from . import ms_blkq4linear_ext
+
+
+class BlkQ4Linear(nn.Module):
+    def __init__(self, block_size, col_wise, scale_only, weights, bias_tensor=None):
+        super().__init__()
+        self.block_size = int(block_size)
+        self.col_wise = bool(col_wise)
+        self.has_offsets = not scale_only
+        self.in_features = weights.size(1)
+        self.out_features = weights.size(0)
+        q_weights, q_scales, q_zp = ms_blkq4linear_ext.quant(
+            self.block_size, self.col_wise, self.has_offsets, weights
+        )
+        self.register_buffer("q_weights", q_weights)
+        self.register_buffer("q_scales", q_scales)
+        self.register_buffer("q_zp", q_zp)
+        self.bias = bias_tensor
+
+    @classmethod
+    def from_packed(cls, block_size, col_wise, in_features, out_features, q_weights, q_scales, q_zp=None,
+                    bias_tensor=None):
+        """Build a layer from tensors produced earlier by ``quant`` (no requantization)."""
+        self = cls.__new__(cls)
+        nn.Module.__init__(self)
+        self.block_size, self.col_wise = int(block_size), bool(col_wise)
+        self.in_features, self.out_features = int(in_features), int(out_features)
+        if q_zp is None:
+            q_zp = torch.empty(0, dtype=torch.uint8, device=q_weights.device)
+        self.has_offsets = q_zp.numel() > 0
+        self.register_buffer("q_weights", q_weights)
+        self.register_buffer("q_scales", q_scales)
+        self.register_buffer("q_zp", q_zp)
+        self.bias = bias_tensor
+        return self
+
+    def forward(self, input, out=None):
+        lead = input.shape[:-1]
+        x = input.reshape(-1, self.in_features)
+        if out is None:
+            output = ms_blkq4linear_ext.forward(
+                self.block_size, self.col_wise, self.in_features, self.out_features,
+                x, self.q_weights, self.q_scales, self.q_zp)
+        else:
+            output = ms_blkq4linear_ext.forward_out(
+                self.block_size, self.col_wise, self.in_features, self.out_features,
+                x, self.q_weights, self.q_scales, self.q_zp, out.view(-1, self.out_features))
+        if self.bias is not None:
+            output += self.bias
+        return output.view(*lead, self.out_features)
+
+    def extra_repr(self):
+        return (f"in_features={self.in_features}, out_features={self.out_features}, block_size={self.block_size}, "
+                f"col_wise={self.col_wise}, has_offsets={self.has_offsets}, bias={self.bias is not None}")

@@ -1,0 +1,88 @@
+"""N-sharded ``BlkQ4Linear`` for one box of B200s: one process per GPU.
+
+The weight [out_features, in_features] is split along out_features (N); rank r owns
+rows [r*N/g, (r+1)*N/g), quantizes and prepacks its shard locally, and computes
+``out_r = input @ W_r^T`` for the replicated input.  The only exchange is an
+all-gather of the outputs along the last dimension at the layer boundary
+(``torch.distributed``, NCCL over NVLink on GPUs; gloo in the CPU tests of the
+partitioning logic).  The reference has no multi-GPU path; this module is the
+partition the W4A16 path shards along.
+
+Quantization blocks never straddle a shard when the shard width is a multiple of
+``shard_multiple(block, col_wise)``; quantizing a shard then yields exactly the
+bytes of the corresponding slice of the full quantized weight.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+
+def shard_multiple(block_size: int, col_wise: bool) -> int:
+    """Shard widths must be multiples of this: 32 (the quantizer's column rule; also
+    covers the 16-column prepack tile) and, row-wise, the block size."""
+    return 32 if col_wise else max(32, block_size)
+
+
+def shard_bounds(out_features: int, world_size: int, rank: int, block_size: int, col_wise: bool):
+    """[n0, n1) of `rank`.  Requires an even split into legal shard widths."""
+    if out_features % world_size != 0:
+        raise ValueError(f"out_features {out_features} does not split evenly over {world_size} ranks")
+    ns = out_features // world_size
+    mult = shard_multiple(block_size, col_wise)
+    if ns % mult != 0:
+        raise ValueError(f"shard width {ns} is not a multiple of {mult} (block {block_size}, col_wise={col_wise})")
+    return rank * ns, (rank + 1) * ns
+
+
+def gather_columns(local_out: torch.Tensor, group=None) -> torch.Tensor:
+    """All-gather [M, N/g] shards into [M, N] (concatenation along the last dim)."""
+    g = dist.get_world_size(group)
+    if g == 1:
+        return local_out
+    M, ns = local_out.shape
+    stacked = torch.empty((g, M, ns), dtype=local_out.dtype, device=local_out.device)
+    dist.all_gather_into_tensor(stacked, local_out.contiguous(), group=group)
+    if M == 1:
+        return stacked.view(1, g * ns)
+    return stacked.permute(1, 0, 2).reshape(M, g * ns)
+
+
+class ShardedBlkQ4Linear(nn.Module):
+    """``BlkQ4Linear`` whose out_features are split over the ranks of ``process_group``.
+
+    ``weights`` is either the full [N, K] weight (each rank slices its rows) or,
+    with ``weights_are_local=True``, this rank's [N/g, K] shard.
+    """
+
+    def __init__(self, block_size, col_wise, scale_only, weights, bias_tensor=None, process_group=None,
+                 weights_are_local=False, gather_output=True):
+        super().__init__()
+        from .ms_blkq4linear import BlkQ4Linear
+
+        self.group = process_group
+        self.world_size = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(process_group) if dist.is_initialized() else 0
+        self.gather_output = gather_output
+        if weights_are_local:
+            local = weights
+            self.out_features = weights.size(0) * self.world_size
+            self.n0 = self.rank * weights.size(0)
+        else:
+            self.out_features = weights.size(0)
+            self.n0, n1 = shard_bounds(self.out_features, self.world_size, self.rank, block_size, col_wise)
+            local = weights[self.n0:n1].contiguous()
+        self.in_features = weights.size(1)
+        self.local = BlkQ4Linear(block_size, col_wise, scale_only, local)
+        self.bias = bias_tensor  # full-width bias, added after the gather
+
+    def forward(self, input):
+        lead = input.shape[:-1]
+        out = self.local(input.reshape(-1, self.in_features))
+        if self.gather_output:
+            out = gather_columns(out, self.group)
+            if self.bias is not None:
+                out += self.bias
+            return out.view(*lead, self.out_features)
+        return out.view(*lead, -1)

@@ -1,0 +1,103 @@
+"""GPU tests of the PyTorch surface (ms_blkq4linear_ext + BlkQ4Linear), the mirror of
+the reference's python/ms_blkq4linear.py and python/ms_blkq4linear_ext."""
+import numpy as np
+import pytest
+
+from oracle import blkq4_oracle as O
+from tests._util import bits, gaussian_act, gaussian_weight
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+def test_ext_quant_matches_oracle_and_returns_empty_zp_when_scale_only():
+    from gemmlib_b200 import ms_blkq4linear_ext as ext
+
+    w = gaussian_weight(96, 128, seed=2)
+    for has_zp in (True, False):
+        qw, qs, qz = ext.quant(32, False, has_zp, w.cuda())
+        pw, ps, pz = O.quant_prepack(32, False, w.numpy(), has_zp)
+        assert qw.dtype == torch.uint8 and qs.dtype == torch.float16 and qz.dtype == torch.uint8
+        assert (qw.cpu().numpy() == pw).all() and (bits(qs.cpu().numpy()) == bits(ps)).all()
+        assert qz.numel() == (pz.size if has_zp else 0)
+        if has_zp:
+            assert (qz.cpu().numpy() == pz).all()
+
+
+def test_reference_usage_script_flow():
+    """The flow of the reference's python/blkq4linear_test.py: known-answer weights for a
+    64 -> 32 layer, row-wise block 32 with offsets; the module must hold the prepacked
+    originals.  (The reference script only prints q_weights; here they are compared.)"""
+    from gemmlib_b200.ms_blkq4linear import BlkQ4Linear
+
+    K, N, block, colwise = 64, 32, 32, False
+    q, s, z = O.kat_generate(block, colwise, K, N, True)
+    w = torch.from_numpy(O.dequant_plain(block, colwise, K, N, q, s, z)).cuda()
+    m = BlkQ4Linear(block, colwise, False, w)
+    assert (m.in_features, m.out_features, m.has_offsets) == (K, N, True)
+    assert (m.q_weights.cpu().numpy() == O.prepack_weights(K, N, q)).all()
+    ps, pz = O.prepack_meta(block, colwise, K, N, s, z)
+    assert (bits(m.q_scales.cpu().numpy()) == bits(ps)).all() and (m.q_zp.cpu().numpy() == pz).all()
+    a = O.kat_activations(8, K)
+    want = O.dequant_gemm(block, colwise, a, N, m.q_weights.cpu().numpy(), ps, pz)
+    got = m(torch.from_numpy(a).cuda()).cpu().numpy()
+    assert (bits(got) == bits(want)).all()
+
+
+@pytest.mark.parametrize("scale_only", [True, False])
+@pytest.mark.parametrize("M", [1, 24])
+def test_forward_with_bias_batch_dims_and_state_dict(scale_only, M):
+    from gemmlib_b200.ms_blkq4linear import BlkQ4Linear
+
+    K, N = 256, 160
+    w = gaussian_weight(N, K, seed=4)
+    bias = torch.linspace(-1, 1, N).to(torch.float16).cuda()
+    m = BlkQ4Linear(64, True, scale_only, w.cuda(), bias)
+    x = gaussian_act(2 * M, K, seed=5).view(2, M, K)
+    y = m(x.cuda())
+    assert y.shape == (2, M, N)
+    pw, ps, pz = O.quant_prepack(64, True, w.numpy(), not scale_only)
+    want = O.dequant_gemm(64, True, x.view(-1, K).numpy(), N, pw, ps, pz).astype(np.float32) + bias.cpu().numpy().astype(np.float32)
+    assert np.abs(y.view(-1, N).cpu().numpy().astype(np.float32) - want).max() <= 1e-2
+    # packed tensors are buffers: they survive a state_dict round trip into a fresh module
+    sd = {k: v.clone() for k, v in m.state_dict().items()}
+    assert set(sd) == {"q_weights", "q_scales", "q_zp"}
+    m2 = BlkQ4Linear.from_packed(64, True, K, N, sd["q_weights"], sd["q_scales"], sd["q_zp"], bias)
+    assert torch.equal(m2(x.cuda()), y)
+
+
+def test_forward_rejects_bad_inputs():
+    from gemmlib_b200.ms_blkq4linear import BlkQ4Linear
+
+    m = BlkQ4Linear(32, True, True, gaussian_weight(64, 128).cuda())
+    with pytest.raises(RuntimeError, match="float16"):
+        m(torch.zeros(2, 128, device="cuda"))
+    with pytest.raises(RuntimeError):
+        m(torch.zeros(2, 64, dtype=torch.float16, device="cuda"))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        m(torch.zeros(2, 128, dtype=torch.float16))
+    with pytest.raises(RuntimeError, match="Cannot block quantize"):
+        BlkQ4Linear(32, True, True, torch.zeros(48, 128, dtype=torch.float16, device="cuda"))
+
+
+def test_forward_in_cuda_graph_on_side_stream():
+    """Calls go to PyTorch's current stream, so a forward can be captured and replayed."""
+    from gemmlib_b200.ms_blkq4linear import BlkQ4Linear
+
+    m = BlkQ4Linear(64, True, True, gaussian_weight(352, 512, seed=9).cuda())
+    for M in (1, 40):
+        x = gaussian_act(M, 512, seed=M).cuda()
+        eager = m(x)
+        out = torch.zeros_like(eager)
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            m(x, out=out)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            m(x, out=out)
+        out.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, eager)
