@@ -25,9 +25,8 @@
 // 16-byte rows-segments of the UMMA operand.  Dequantization numerics are the
 // reference kernel's (fp16(16+q) by bit trick, fma.rn.f16 with rn(scale*(-16-zp));
 // src/mickey/cutlass_ext/q4gemm/warp/quantb_meta_mma_tensor_op_tile_iterator.h:69-104, :436-543).
-#include <cuda.h>
-
 #include "blkq4_common.cuh"
+#include "blkq4_tma.cuh"
 
 namespace blkq4 {
 
@@ -61,53 +60,9 @@ struct Params {
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false when the wait was given up (here or elsewhere in the CTA).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int who) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  for (;;) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitCycles) {
-      *abort_flag = 1;
-      atomicCAS(&g_gemm_tc_error, 0, who);
-      return false;
-    }
-  }
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
-                                            uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+// Bounded wait on an mbarrier; see mbar_wait_bounded.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int who) {
+  return mbar_wait_bounded(bar, parity, abort_flag, &g_gemm_tc_error, who, kWaitCycles);
 }
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -227,7 +182,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       mbar_init(bar(BAR_ACC_EMPTY + i), kNumEpiWarps);
     }
     *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_init_fence();
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -451,36 +406,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
 
 // ---- host side ---------------------------------------------------------------------------
 
-using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                              CUtensorMapFloatOOBfill);
-
-EncodeFn get_encode_fn() {
-  static EncodeFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      p = nullptr;
-    return reinterpret_cast<EncodeFn>(p);
-  }();
-  return fn;
-}
-
-// 2-D row-major tensor [rows][cols] of `elt` bytes per element; box = box_rows x box_cols.
-bool encode_2d(CUtensorMap* map, CUtensorMapDataType dt, int elt, const void* ptr, uint64_t cols,
-               uint64_t rows, uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle swz) {
-  EncodeFn fn = get_encode_fn();
-  if (!fn) return false;
-  cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {cols * (uint64_t)elt};
-  cuuint32_t box[2] = {box_cols, box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  return fn(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 }  // namespace
 
 std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
@@ -495,25 +420,25 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
   p.out = out;
 
   CUtensorMap tm_act, tm_pack, tm_scale, tm_zp;
-  bool ok = encode_2d(&tm_act, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a, (uint64_t)K, (uint64_t)M, BLOCK_K,
+  bool ok = encode_tensor_map_2d(&tm_act, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a, (uint64_t)K, (uint64_t)M, BLOCK_K,
                       (uint32_t)p.BM, CU_TENSOR_MAP_SWIZZLE_128B);
-  ok = ok && encode_2d(&tm_pack, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, packed, (uint64_t)K, (uint64_t)(N / 2),
+  ok = ok && encode_tensor_map_2d(&tm_pack, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, packed, (uint64_t)K, (uint64_t)(N / 2),
                        BLOCK_K, TILE_N / 2, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (colwise) {
     p.meta_rows = block >= BLOCK_K ? 1 : BLOCK_K / block;
     p.meta_row_bytes_s = TILE_N * 2;
     p.meta_row_bytes_z = TILE_N;
-    ok = ok && encode_2d(&tm_scale, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, scales, (uint64_t)N,
+    ok = ok && encode_tensor_map_2d(&tm_scale, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, scales, (uint64_t)N,
                          (uint64_t)(K / block), TILE_N, (uint32_t)p.meta_rows, CU_TENSOR_MAP_SWIZZLE_NONE);
-    ok = ok && encode_2d(&tm_zp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, zp ? zp : packed, (uint64_t)N,
+    ok = ok && encode_tensor_map_2d(&tm_zp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, zp ? zp : packed, (uint64_t)N,
                          (uint64_t)(K / block), TILE_N, (uint32_t)p.meta_rows, CU_TENSOR_MAP_SWIZZLE_NONE);
   } else {
     p.meta_rows = block >= TILE_N ? 1 : TILE_N / block;
     p.meta_row_bytes_s = BLOCK_K * 2;
     p.meta_row_bytes_z = BLOCK_K;
-    ok = ok && encode_2d(&tm_scale, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, scales, (uint64_t)K,
+    ok = ok && encode_tensor_map_2d(&tm_scale, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, scales, (uint64_t)K,
                          (uint64_t)(N / block), BLOCK_K, (uint32_t)p.meta_rows, CU_TENSOR_MAP_SWIZZLE_NONE);
-    ok = ok && encode_2d(&tm_zp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, zp ? zp : packed, (uint64_t)K,
+    ok = ok && encode_tensor_map_2d(&tm_zp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, zp ? zp : packed, (uint64_t)K,
                          (uint64_t)(N / block), BLOCK_K, (uint32_t)p.meta_rows, CU_TENSOR_MAP_SWIZZLE_NONE);
   }
   if (!ok) return "cuTensorMapEncodeTiled failed";

@@ -114,6 +114,31 @@ def dequant(block, colwise, K, N, packed, scales, zp, kernel_formula: bool = Fal
     return out
 
 
+def dequant_ideal(block, colwise, K, N, packed, scales, zp):
+    """Packed form -> float64 [N, K] of scale * (q - zp) with no fp16 rounding at all:
+    the value both fp16 dequantization formulas approximate."""
+    bk, bn = blocking(block, colwise)
+    k = np.arange(K)
+    n = np.arange(N)
+    kk, nn = k % 16, n % 16
+    kp = 16 * (k // 16) + 4 * ((kk % 8) // 2) + 2 * (kk & 1)          # + nhi
+    np_ = 8 * (n // 16) + nn % 8
+    byte = packed.reshape(N // 2, K)[np_[:, None], kp[None, :] + (nn // 8)[:, None]]
+    q = np.where((kk // 8)[None, :] == 1, byte >> 4, byte & 0xF).astype(np.int64)
+    if colwise:
+        mi = (k // block)[None, :] * N + n[:, None]
+        mi_z = mi
+    else:
+        r = k % 16
+        t, hi, odd = (r % 8) // 2, r // 8, r & 1
+        base = (n // block)[:, None] * K + (k // 16 * 16)[None, :]
+        mi = base + (4 * t + 2 * hi + odd)[None, :]
+        mi_z = base + (4 * t + 2 * odd + hi)[None, :]
+    s = scales.astype(np.float64)[mi]
+    z = zp.astype(np.int64)[mi_z] if zp is not None else 8
+    return s * (q - z)
+
+
 def gemm(a_mk: np.ndarray, wdq_nk: np.ndarray):
     """fp16 [M,K] x fp16 [N,K]^T -> fp16 [M,N], fp32 accumulation."""
     M, K = a_mk.shape
