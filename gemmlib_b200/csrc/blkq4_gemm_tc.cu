@@ -14,8 +14,9 @@
 //   warp 1      MMA issuer (one elected lane); owns the TMEM allocation
 //   warps 2-5   epilogue: tcgen05.ld -> fp16 -> global, overlapped with the next tile
 //               through a second TMEM accumulator buffer
-//   warps 6-13  dequantizers: one 16-byte chunk (16 k x 2 n) per thread and step,
-//               written as fp16 in the K-major 128-byte-swizzled operand layout
+//   warps 6-13  dequantizers, two groups of four warps on alternate steps: two 16-byte
+//               chunks (16 k x 2 n each) per thread and step, written as fp16 in the
+//               K-major 128-byte-swizzled operand layout
 // Stages are handed over with mbarriers; every wait is bounded and, on expiry, sets
 // an error word and drains the CTA instead of hanging the GPU.
 //
@@ -38,8 +39,10 @@ constexpr int TILE_N = 128;       // weight columns per tile (UMMA M)
 constexpr int BLOCK_K = 64;       // k per pipeline step: one 128-byte swizzle row of fp16
 constexpr int UMMA_K = 16;
 constexpr int kStages = 4;        // TMA ring
-constexpr int kDeqStages = 3;     // dequantized-weight ring
+constexpr int kDeqStages = 4;     // dequantized-weight ring
 constexpr int kNumDeqWarps = 8;
+constexpr int kDeqGroups = 2;     // warp groups taking alternate k steps
+constexpr int kWarpsPerDeqGroup = kNumDeqWarps / kDeqGroups;
 constexpr int kNumEpiWarps = 4;
 constexpr int kThreads = 32 * (2 + kNumEpiWarps + kNumDeqWarps);
 constexpr int kDeqTileBytes = TILE_N * BLOCK_K * 2;  // 16 KB
@@ -171,10 +174,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
       mbar_init(bar(BAR_FULL + i), 1);
-      mbar_init(bar(BAR_EMPTY + i), 1 + kNumDeqWarps);
+      mbar_init(bar(BAR_EMPTY + i), 1 + kWarpsPerDeqGroup);
     }
     for (int i = 0; i < kDeqStages; ++i) {
-      mbar_init(bar(BAR_DEQ_FULL + i), kNumDeqWarps);
+      mbar_init(bar(BAR_DEQ_FULL + i), kWarpsPerDeqGroup);
       mbar_init(bar(BAR_DEQ_EMPTY + i), 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -296,30 +299,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     }
   } else {
     // =============================== dequantizers ===============================
-    // Thread t of the 256: packed column np_l = t / 4 of the tile, 16-byte chunk kc = t % 4
-    // of its 64 bytes -> k in [16 kc, 16 kc + 16) of tile rows na = 16 (np_l / 8) + np_l % 8
-    // and na + 8.  Output: per row two 16-byte units (k 0-7 and 8-15 of the chunk) at
-    // unit index 2 kc and 2 kc + 1, XOR-swizzled with row % 8.
-    const int t = threadIdx.x - 32 * (2 + kNumEpiWarps);
-    const int np_l = t >> 2, kc = t & 3;
-    const int na = 16 * (np_l >> 3) + (np_l & 7), nb = na + 8;
-    const uint32_t row_a = (uint32_t)na * 128u, row_b = (uint32_t)nb * 128u;
-    const uint32_t u0a = (uint32_t)(((2 * kc) ^ (na & 7)) << 4), u1a = (uint32_t)(((2 * kc + 1) ^ (na & 7)) << 4);
-    const uint32_t u0b = (uint32_t)(((2 * kc) ^ (nb & 7)) << 4), u1b = (uint32_t)(((2 * kc + 1) ^ (nb & 7)) << 4);
-    uint32_t it = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      for (int ks = 0; ks < k_steps; ++ks, ++it) {
-        const int s = it % kStages, d = it % kDeqStages;
-        if (!mbar_wait(bar(BAR_FULL + s), (it / kStages) & 1, abort_flag, 0x400 | s)) goto deq_done;
-        if (it >= (uint32_t)kDeqStages &&
-            !mbar_wait(bar(BAR_DEQ_EMPTY + d), ((it / kDeqStages) - 1) & 1, abort_flag, 0x410 | d))
-          goto deq_done;
-
-        const uint8_t* pk = base_ptr + plan.pack + s * kPackTileBytes;
-        const uint4 wv = *reinterpret_cast<const uint4*>(pk + t * 16);
+    // Two groups of four warps take alternate 64-k steps, so that a group has two step times
+    // for the dependent chain wait -> load -> convert -> store -> fence -> arrive of one step.
+    // A step's packed tile is 256 chunks of 16 bytes; thread t of a group converts chunks
+    // t and t + 128.  Chunk c: packed column np_l = c / 4 of the tile, 16-byte chunk
+    // kc = c % 4 of its 64 bytes -> k in [16 kc, 16 kc + 16) of tile rows
+    // na = 16 (np_l / 8) + np_l % 8 and na + 8.  Output: per row two 16-byte units (k 0-7
+    // and 8-15 of the chunk) at unit index 2 kc and 2 kc + 1, XOR-swizzled with row % 8.
+    const int dt = threadIdx.x - 32 * (2 + kNumEpiWarps);
+    const int group = dt >> 7, t = dt & 127;
+    int my_tiles = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) ++my_tiles;
+    const uint32_t total_its = (uint32_t)my_tiles * (uint32_t)k_steps;
+    for (uint32_t it = group; it < total_its; it += kDeqGroups) {
+      const int s = it % kStages, d = it % kDeqStages;
+      if (!mbar_wait(bar(BAR_FULL + s), (it / kStages) & 1, abort_flag, 0x400 | s)) break;
+      if (it >= (uint32_t)kDeqStages &&
+          !mbar_wait(bar(BAR_DEQ_EMPTY + d), ((it / kDeqStages) - 1) & 1, abort_flag, 0x410 | d))
+        break;
+      const uint8_t* pk = base_ptr + plan.pack + s * kPackTileBytes;
+      const uint8_t* sc_tile = base_ptr + plan.scale + s * kScaleTileBytes;
+      const uint8_t* zp_tile = base_ptr + plan.zp + s * kZpTileBytes;
+      uint8_t* dq = base_ptr + plan.deq + d * kDeqTileBytes;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int c = t + 128 * half;
+        const int np_l = c >> 2, kc = c & 3;
+        const int na = 16 * (np_l >> 3) + (np_l & 7), nb = na + 8;
+        const uint4 wv = *reinterpret_cast<const uint4*>(pk + c * 16);
         const uint32_t w4[4] = {wv.x, wv.y, wv.z, wv.w};
-        const uint8_t* sc_tile = base_ptr + plan.scale + s * kScaleTileBytes;
-        const uint8_t* zp_tile = base_ptr + plan.zp + s * kZpTileBytes;
 
         uint32_t s_lo_a[4], s_hi_a[4], o_lo_a[4], o_hi_a[4];
         uint32_t s_lo_b[4], s_hi_b[4], o_lo_b[4], o_hi_b[4];
@@ -375,21 +383,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
           b_lo[r] = hfma2_u32(s_lo_b[r], h[2], o_lo_b[r]);
           b_hi[r] = hfma2_u32(s_hi_b[r], h[3], o_hi_b[r]);
         }
-        uint8_t* dq = base_ptr + plan.deq + d * kDeqTileBytes;
-        *reinterpret_cast<uint4*>(dq + row_a + u0a) = make_uint4(a_lo[0], a_lo[1], a_lo[2], a_lo[3]);
-        *reinterpret_cast<uint4*>(dq + row_a + u1a) = make_uint4(a_hi[0], a_hi[1], a_hi[2], a_hi[3]);
-        *reinterpret_cast<uint4*>(dq + row_b + u0b) = make_uint4(b_lo[0], b_lo[1], b_lo[2], b_lo[3]);
-        *reinterpret_cast<uint4*>(dq + row_b + u1b) = make_uint4(b_hi[0], b_hi[1], b_hi[2], b_hi[3]);
-
-        fence_proxy_async();  // generic-proxy writes -> visible to the tensor core (async proxy)
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(bar(BAR_DEQ_FULL + d));
-          mbar_arrive(bar(BAR_EMPTY + s));
-        }
+        const uint32_t row_a = (uint32_t)na * 128u, row_b = (uint32_t)nb * 128u;
+        const uint32_t sw_a = (uint32_t)(na & 7), sw_b = (uint32_t)(nb & 7);
+        *reinterpret_cast<uint4*>(dq + row_a + (((2 * kc) ^ sw_a) << 4)) = make_uint4(a_lo[0], a_lo[1], a_lo[2], a_lo[3]);
+        *reinterpret_cast<uint4*>(dq + row_a + (((2 * kc + 1) ^ sw_a) << 4)) = make_uint4(a_hi[0], a_hi[1], a_hi[2], a_hi[3]);
+        *reinterpret_cast<uint4*>(dq + row_b + (((2 * kc) ^ sw_b) << 4)) = make_uint4(b_lo[0], b_lo[1], b_lo[2], b_lo[3]);
+        *reinterpret_cast<uint4*>(dq + row_b + (((2 * kc + 1) ^ sw_b) << 4)) = make_uint4(b_hi[0], b_hi[1], b_hi[2], b_hi[3]);
+      }
+      fence_proxy_async();  // generic-proxy writes -> visible to the tensor core (async proxy)
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(bar(BAR_DEQ_FULL + d));
+        mbar_arrive(bar(BAR_EMPTY + s));
       }
     }
-  deq_done:;
   }
 
   // ---- teardown ----
