@@ -330,14 +330,11 @@ def run_ours(args):
         line["roofline"] = {
             "bound": "hbm", "achieved": round(nbytes / (launch_us * 1e-6) / 1e9, 2), "peak": peaks["hbm_gbs"],
             "unit": "GB/s", "frac": round(nbytes / (launch_us * 1e-6) / 1e9 / peaks["hbm_gbs"], 4),
-            "traffic": TRAFFIC_BYTES_PER_LAUNCH, "kernel": "gemv_kernel<1,1,4,true>",
+            "traffic": TRAFFIC_BYTES_PER_LAUNCH, "kernel": "gemv_persistent_kernel<1,false>",
             "bytes_per_launch": nbytes, "us_per_launch": round(launch_us, 3), "peak_source": peaks["source"],
         }
     if world == 1:
-        line["quant_prepack"] = {
-            "GB/s": round((2 * K * N + K * N // 2 + 2 * (K // cfg["block"]) * N) / (statistics.median(quant_ms) * 1e-3) / 1e9, 1),
-            "ms_per_layer": round(statistics.median(quant_ms), 4),
-            "note": "single calls through BlkQ4Linear.__init__ (includes allocation), c2 layer"}
+        line["quant_prepack"] = bench_quant(torch, dev, peaks)
         line["gemm"] = bench_gemm_c3(torch, dev, peaks)
         gbs, sec, passes, threads = cpu_dequant_gemm_sample(cfg)
         line["cpu_baseline"] = {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port",
@@ -349,8 +346,39 @@ def run_ours(args):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the timed kernel, from the
-# committed ncu capture (profiles/); None until a capture exists.
-TRAFFIC_BYTES_PER_LAUNCH = None
+# committed ncu capture (profiles/gemv_persistent_c2.md): 23,988,736 B read, 0 B written
+# (the 22 KB of output stay in L2 within the captured launch).
+TRAFFIC_BYTES_PER_LAUNCH = 23988736
+
+
+def bench_quant(torch, dev, peaks):
+    """Quantize + prepack of c2-shaped layers (fp16 source rotating over > L2), kernel only."""
+    from gemmlib_b200 import capi
+
+    c = C2
+    K, N, block = c["K"], c["N"], c["block"]
+    wb, me = capi.quant_size(block, True, K, N)
+    srcs = [(torch.randn(N, K, device=dev) * c["sigma"]).half() for _ in range(4)]  # 4 x 90 MB
+    qw = torch.empty(wb, dtype=torch.uint8, device=dev)
+    qs = torch.empty(me, dtype=torch.float16, device=dev)
+    for w in srcs:
+        capi.quant(block, True, K, N, K, w, qw, qs, None)
+    torch.cuda.synchronize()
+    reps = 10
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        for w in srcs:
+            capi.quant(block, True, K, N, K, w, qw, qs, None)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (reps * len(srcs))
+    nbytes = 2 * K * N + K * N // 2 + 2 * me
+    gbs = nbytes / us / 1e3
+    return {"workload": "quantize+prepack of one c2 layer (4096 x 11008 fp16 -> int4 block 64 symmetric)",
+            "value": round(gbs, 1), "unit": "GB/s", "us_per_call": round(us, 2),
+            "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(gbs / peaks["hbm_gbs"], 4), "peak_source": peaks["source"]}}
 
 
 def bench_gemm_c3(torch, dev, peaks):
@@ -388,14 +416,56 @@ def bench_gemm_c3(torch, dev, peaks):
             "frac_of_nominal_2250": round(tf / 2250.0, 4)}
 
 
+def run_profile_case(args):
+    """A few plain launches of ONE kernel over rotating inputs larger than L2 but small
+    enough for a profiler capture (no graph, no timing loop); the commands in profiles/
+    wrap this in ncu.  Prints nothing the benchmark contract uses."""
+    import torch
+
+    from gemmlib_b200 import capi
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    c = dict(gemv=C2, gemm=C3, quant=C3)[args.profile]
+    sets = dict(gemv=6, gemm=4, quant=8)[args.profile]
+    M, K, N, block, cw = c["M"], c["K"], c["N"], c["block"], c["col_wise"]
+    wb, me = capi.quant_size(block, cw, K, N)
+    ws, packed = [], []
+    for i in range(sets):
+        w = (torch.randn(N, K, device=dev) * c["sigma"]).half()
+        qw = torch.empty(wb, dtype=torch.uint8, device=dev)
+        qs = torch.empty(me, dtype=torch.float16, device=dev)
+        qz = torch.empty(me, dtype=torch.uint8, device=dev) if c["has_zp"] else None
+        capi.quant(block, cw, K, N, K, w, qw, qs, qz)
+        packed.append((qw, qs, qz))
+        ws.append(w if args.profile == "quant" else None)
+    a = torch.randn(M, K, device=dev).half()
+    out = torch.empty(M, N, dtype=torch.float16, device=dev)
+    torch.cuda.synchronize()
+    for i in range(args.launches):
+        qw, qs, qz = packed[i % sets]
+        if args.profile == "quant":
+            capi.quant(block, cw, K, N, K, ws[i % sets], qw, qs, qz)
+        else:
+            capi.gemm(block, cw, M, N, K, a, qw, qs, qz, out)
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_case": args.profile, "launches": args.launches, "sets": sets,
+                      "kernel_status": capi.last_kernel_status()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=int(os.environ.get("WORLD_SIZE", "1")))
     ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--profile", choices=["gemv", "gemm", "quant"], default=None,
+                    help="profiling driver: a few plain launches of one kernel (see profiles/)")
+    ap.add_argument("--launches", type=int, default=8)
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.profile:
+        run_profile_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -42,11 +42,12 @@ def gather_columns(local_out: torch.Tensor, group=None) -> torch.Tensor:
     if g == 1:
         return local_out
     M, ns = local_out.shape
-    stacked = torch.empty((g, M, ns), dtype=local_out.dtype, device=local_out.device)
+    # rank r's [M, ns] block lands at rows [r*M, (r+1)*M) of the gather buffer
+    stacked = torch.empty((g * M, ns), dtype=local_out.dtype, device=local_out.device)
     dist.all_gather_into_tensor(stacked, local_out.contiguous(), group=group)
     if M == 1:
         return stacked.view(1, g * ns)
-    return stacked.permute(1, 0, 2).reshape(M, g * ns)
+    return stacked.view(g, M, ns).permute(1, 0, 2).reshape(M, g * ns)
 
 
 class ShardedBlkQ4Linear(nn.Module):
