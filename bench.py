@@ -182,6 +182,11 @@ def workload_config(n_gpus):
 # our arm
 
 
+def _log(msg):
+    """Progress marker on stderr (the JSON line on stdout stays alone)."""
+    print(f"[bench r{os.environ.get('RANK', '0')} {time.strftime('%H:%M:%S')}] {msg}", file=sys.stderr, flush=True)
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -200,6 +205,7 @@ def run_ours(args):
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
+    _log(f"process group ready, world {world}")
     peaks = measured_peaks()
     cfg = C2
     M, K, N = cfg["M"], cfg["K"], cfg["N"]
@@ -222,6 +228,7 @@ def run_ours(args):
         torch.cuda.synchronize()
         quant_ms.append(e0.elapsed_time(e1))
         del w
+    _log("layers quantized")
     g = torch.Generator().manual_seed(0)
     a_host = torch.randn(M, K, generator=g).to(torch.float16).pin_memory()
     a_dev = a_host.to(dev)
@@ -241,11 +248,13 @@ def run_ours(args):
         for _ in range(3):
             step_resident()
     torch.cuda.synchronize()
+    _log("eager warm-up done, capturing graph")
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph, stream=stream):
         step_resident()
     torch.cuda.synchronize()
 
+    _log("graph captured")
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -272,6 +281,7 @@ def run_ours(args):
         t = torch.tensor([ms], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
+    _log(f"timed region done: {ms:.3f} ms")
     status = capi.last_kernel_status()
 
     nbytes = algorithmic_bytes(M, K, N, cfg["block"], cfg["col_wise"], cfg["has_zp"])
@@ -305,6 +315,7 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     e2e_value = nbytes * LAYERS * e2e_steps * world / (e2e_ms * 1e-3) / 1e9
+    _log("end-to-end region done")
 
     line = {
         "metric": "W4A16 effective HBM GB/s (M<=16)", "value": round(value, 2), "unit": "GB/s",
