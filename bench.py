@@ -351,9 +351,20 @@ def run_ours(args):
         line["cpu_baseline"] = {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port",
                                 "sample": f"one c2 layer, {passes} passes of oracle dequantize+GEMV, median {sec * 1e3:.1f} ms per pass"}
     if rank == 0:
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Tear down in order: the captured graph holds NCCL kernels, so it goes first.  A
+        # communicator teardown that does not return (seen with graph-captured collectives)
+        # must not turn a finished measurement into a hung job: give it 20 s, then leave.
+        del graph
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = threading.Thread(target=dist.destroy_process_group, daemon=True)
+        t.start()
+        t.join(timeout=20)
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the timed kernel, from the
