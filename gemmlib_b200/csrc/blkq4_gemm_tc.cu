@@ -6,7 +6,12 @@
 // M side, up to 256 activation rows its N side, so one dequantized weight element
 // feeds 256 multiply-adds and small M wastes no tensor work.
 //
-//   D^T[128 n x BM m] (TMEM, fp32)  +=  Wdq^T[128 n x 64 k] (smem)  x  A[BM m x 64 k]^T (smem)
+//   D^T[128 n x BM m] (TMEM, fp32)  +=  Wdq^T[128 n x 64 k] (TMEM, fp16)  x  A[BM m x 64 k]^T (smem)
+//
+// The dequantized weights never touch shared memory: the dequantizer threads write them
+// straight into tensor memory (tcgen05.st) and the MMA takes its first operand from there.
+// Measured with the operand staged in shared memory instead, the 16 KB written plus 16 KB
+// re-read per step, on top of the TMA traffic, cost a third of the step time.
 //
 // Persistent CTAs (one per SM) walk the tile list.  Warp roles:
 //   warp 0      TMA producer: per 64-k step one activation tile (128-byte swizzle),
@@ -14,16 +19,15 @@
 //   warp 1      MMA issuer (one elected lane); owns the TMEM allocation
 //   warps 2-5   epilogue: tcgen05.ld -> fp16 -> global, overlapped with the next tile
 //               through a second TMEM accumulator buffer
-//   warps 6-13  dequantizers, two groups of four warps on alternate steps: two 16-byte
-//               chunks (16 k x 2 n each) per thread and step, written as fp16 in the
-//               K-major 128-byte-swizzled operand layout
+//   warps 6-13  dequantizers, two groups of four warps on alternate steps: thread = one
+//               weight column n of the tile (TMEM lane n), 64 k per step = 32 TMEM columns
 // Stages are handed over with mbarriers; every wait is bounded and, on expiry, sets
 // an error word and drains the CTA instead of hanging the GPU.
 //
 // The packed weight layout was designed for mma.sync register fragments (reference
 // src/mickey/blk_q4/f16_quant_sm80.cuh:362-417); a 16-byte run of a packed column
-// still holds 16 consecutive k of two columns, which dequantizes into four
-// 16-byte rows-segments of the UMMA operand.  Dequantization numerics are the
+// still holds 16 consecutive k of two columns n0, n0 + 8, so the threads of columns n0 and
+// n0 + 8 read the same 64 bytes per step and each keeps its own nibbles.  Dequantization numerics are the
 // reference kernel's (fp16(16+q) by bit trick, fma.rn.f16 with rn(scale*(-16-zp));
 // src/mickey/cutlass_ext/q4gemm/warp/quantb_meta_mma_tensor_op_tile_iterator.h:69-104, :436-543).
 #include "blkq4_common.cuh"
@@ -38,14 +42,14 @@ namespace {
 constexpr int TILE_N = 128;       // weight columns per tile (UMMA M)
 constexpr int BLOCK_K = 64;       // k per pipeline step: one 128-byte swizzle row of fp16
 constexpr int UMMA_K = 16;
-constexpr int kStages = 4;        // TMA ring
-constexpr int kDeqStages = 4;     // dequantized-weight ring
+constexpr int kStages = 5;        // TMA ring (shared memory) = dequantized-weight ring (tensor memory)
+constexpr int kDeqStages = kStages;
+constexpr int kDeqCols = BLOCK_K / 2;  // TMEM columns of one dequantized stage: 2 fp16 per column
 constexpr int kNumDeqWarps = 8;
 constexpr int kDeqGroups = 2;     // warp groups taking alternate k steps
 constexpr int kWarpsPerDeqGroup = kNumDeqWarps / kDeqGroups;
 constexpr int kNumEpiWarps = 4;
 constexpr int kThreads = 32 * (2 + kNumEpiWarps + kNumDeqWarps);
-constexpr int kDeqTileBytes = TILE_N * BLOCK_K * 2;  // 16 KB
 constexpr int kPackTileBytes = (TILE_N / 2) * BLOCK_K;  // 4 KB: 64 packed columns x 64 bytes
 constexpr int kScaleTileBytes = 1024;
 constexpr int kZpTileBytes = 512;
@@ -57,6 +61,9 @@ struct Params {
   int m_tiles, n_tiles;
   int has_zp;
   int meta_rows;     // rows of the scale / zero-point box per step
+  int acc_bufs;      // TMEM accumulator buffers: 2 when 2*BM + the dequantized stages fit in 512 columns
+  int a_col0;        // first TMEM column of the dequantized stages
+  uint32_t tmem_cols;  // allocation: power of two >= acc_bufs*BM + kDeqStages*kDeqCols
   uint32_t meta_row_bytes_s, meta_row_bytes_z;  // bytes per box row
   __half* out;
 };
@@ -73,14 +80,29 @@ __device__ __forceinline__ void tc_fence_before() {
 __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                         uint32_t idesc, uint32_t accumulate) {
+// First operand from tensor memory: 128 lanes (rows) x 8 columns per 16 k, two fp16 per column.
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
@@ -121,14 +143,13 @@ __host__ __device__ inline uint32_t make_idesc_f16(int umma_m, int umma_n) {
 // ---- shared-memory plan ---------------------------------------------------------------------
 
 struct SmemPlan {
-  uint32_t act, pack, scale, zp, deq, bars, total;
+  uint32_t act, pack, scale, zp, bars, total;
   uint32_t act_bytes;
 };
 __host__ __device__ inline SmemPlan make_plan(int BM) {
   SmemPlan p;
   p.act_bytes = (uint32_t)BM * 128u;
   uint32_t o = 0;
-  p.deq = o;   o += kDeqStages * kDeqTileBytes;                     // 1024-aligned tiles
   p.act = o;   o += kStages * ((p.act_bytes + 1023u) & ~1023u);     // 1024-aligned tiles
   p.pack = o;  o += kStages * kPackTileBytes;
   p.scale = o; o += kStages * kScaleTileBytes;
@@ -138,13 +159,14 @@ __host__ __device__ inline SmemPlan make_plan(int BM) {
   return p;
 }
 
-// Barrier slots (8 bytes each) inside the barrier block.
+// Barrier slots (8 bytes each) inside the barrier block.  Stage s of the TMA ring and stage s
+// of the dequantized ring belong to the same k step, so one "MMA done" barrier frees both.
 enum : int {
-  BAR_FULL = 0,                           // [kStages]    TMA data landed
-  BAR_EMPTY = BAR_FULL + kStages,         // [kStages]    stage consumed (MMA commit + dequant warps)
-  BAR_DEQ_FULL = BAR_EMPTY + kStages,     // [kDeqStages] dequantized tile written
-  BAR_DEQ_EMPTY = BAR_DEQ_FULL + kDeqStages,  // [kDeqStages] MMAs reading it retired
-  BAR_ACC_FULL = BAR_DEQ_EMPTY + kDeqStages,  // [2] accumulator complete
+  BAR_FULL = 0,                           // [kStages] TMA data landed (producer -> dequantizers)
+  BAR_PACK_FREE = BAR_FULL + kStages,     // [kStages] packed weights / meta read (dequantizers -> producer)
+  BAR_DEQ_FULL = BAR_PACK_FREE + kStages, // [kStages] dequantized stage written to TMEM (-> MMA issuer)
+  BAR_MMA_DONE = BAR_DEQ_FULL + kStages,  // [kStages] the step's MMAs retired (-> producer, dequantizers)
+  BAR_ACC_FULL = BAR_MMA_DONE + kStages,  // [2] accumulator complete
   BAR_ACC_EMPTY = BAR_ACC_FULL + 2,       // [2] accumulator drained by the epilogue
   BAR_COUNT = BAR_ACC_EMPTY + 2
 };
@@ -168,17 +190,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_tiles = p.m_tiles * p.n_tiles;
   const int k_steps = p.K / BLOCK_K;
-  const uint32_t tmem_cols = (2 * p.BM <= 32) ? 32u : (2 * p.BM <= 64) ? 64u : (2 * p.BM <= 128) ? 128u
-                             : (2 * p.BM <= 256) ? 256u : 512u;
+  const uint32_t tmem_cols = p.tmem_cols;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
       mbar_init(bar(BAR_FULL + i), 1);
-      mbar_init(bar(BAR_EMPTY + i), 1 + kWarpsPerDeqGroup);
-    }
-    for (int i = 0; i < kDeqStages; ++i) {
+      mbar_init(bar(BAR_PACK_FREE + i), kWarpsPerDeqGroup);
       mbar_init(bar(BAR_DEQ_FULL + i), kWarpsPerDeqGroup);
-      mbar_init(bar(BAR_DEQ_EMPTY + i), 1);
+      mbar_init(bar(BAR_MMA_DONE + i), 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(BAR_ACC_FULL + i), 1);
@@ -210,7 +229,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
           const int s = it % kStages;
           if (it >= (uint32_t)kStages &&
-              !mbar_wait(bar(BAR_EMPTY + s), ((it / kStages) - 1) & 1, abort_flag, 0x100 | s))
+              (!mbar_wait(bar(BAR_MMA_DONE + s), ((it / kStages) - 1) & 1, abort_flag, 0x100 | s) ||
+               !mbar_wait(bar(BAR_PACK_FREE + s), ((it / kStages) - 1) & 1, abort_flag, 0x110 | s)))
             goto producer_done;
           const uint32_t fb = bar(BAR_FULL + s);
           mbar_arrive_expect_tx(fb, tx);
@@ -239,28 +259,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       const uint32_t idesc = make_idesc_f16(TILE_N, p.BM);
       uint32_t it = 0, tcount = 0;
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
-        const int ab = tcount & 1;
-        if (tcount >= 2 &&
-            !mbar_wait(bar(BAR_ACC_EMPTY + ab), ((tcount >> 1) - 1) & 1, abort_flag, 0x200 | ab))
+        const int ab = tcount % p.acc_bufs;
+        if (tcount >= (uint32_t)p.acc_bufs &&
+            !mbar_wait(bar(BAR_ACC_EMPTY + ab), ((tcount / p.acc_bufs) - 1) & 1, abort_flag, 0x200 | ab))
           goto mma_done;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(ab * p.BM);
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
-          const int s = it % kStages, d = it % kDeqStages;
-          if (!mbar_wait(bar(BAR_FULL + s), (it / kStages) & 1, abort_flag, 0x210 | s)) goto mma_done;
-          if (!mbar_wait(bar(BAR_DEQ_FULL + d), (it / kDeqStages) & 1, abort_flag, 0x220 | d))
-            goto mma_done;
+          const int s = it % kStages;
+          // The dequantizers waited for the step's TMA data before writing TMEM, so this one
+          // wait also covers the activation tile.  The issuing thread is the serial bottleneck
+          // of the pipeline (one wait, four MMAs, one commit per step must fit in the ~540
+          // cycles the MMAs take), hence a single barrier in and a single commit out.
+          if (!mbar_wait(bar(BAR_DEQ_FULL + s), (it / kStages) & 1, abort_flag, 0x220 | s)) goto mma_done;
           tc_fence_after();
-          const uint32_t a_addr = base + plan.deq + d * kDeqTileBytes;
-          const uint32_t b_addr = base + plan.act + s * act_stride;
-#pragma unroll
-          for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-            // 16 k = 32 bytes further along the swizzled row
-            umma_f16(d_tmem, make_sw128_kmajor_desc(a_addr + k * 32), make_sw128_kmajor_desc(b_addr + k * 32),
-                     idesc, (ks > 0 || k > 0) ? 1u : 0u);
+          const uint32_t a_tmem = tmem_base + (uint32_t)(p.a_col0 + s * kDeqCols);
+          const uint64_t b_desc = make_sw128_kmajor_desc(base + plan.act + s * act_stride);
+          if (ks == 0) {
+            umma_f16_ts(d_tmem, a_tmem, b_desc, idesc, 0u);
+          } else {
+            umma_f16_ts(d_tmem, a_tmem, b_desc, idesc, 1u);
           }
-          umma_commit(bar(BAR_EMPTY + s));
-          umma_commit(bar(BAR_DEQ_EMPTY + d));
+#pragma unroll
+          for (int k = 1; k < BLOCK_K / UMMA_K; ++k) {
+            // 16 k = 8 TMEM columns of the weights, 32 bytes (2 descriptor units) of the activation row
+            umma_f16_ts(d_tmem, a_tmem + k * (UMMA_K / 2), b_desc + (uint64_t)(2 * k), idesc, 1u);
+          }
+          umma_commit(bar(BAR_MMA_DONE + s));
         }
         umma_commit(bar(BAR_ACC_FULL + ab));
       }
@@ -275,8 +300,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     uint32_t tcount = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
       const int n_tile = tile / p.m_tiles, m_tile = tile % p.m_tiles;
-      const int ab = tcount & 1;
-      if (!mbar_wait(bar(BAR_ACC_FULL + ab), (tcount >> 1) & 1, abort_flag, 0x300 | ab)) break;
+      const int ab = tcount % p.acc_bufs;
+      if (!mbar_wait(bar(BAR_ACC_FULL + ab), (tcount / p.acc_bufs) & 1, abort_flag, 0x300 | ab)) break;
       tc_fence_after();
       const int n = n_tile * TILE_N + quarter * 32 + lane;
       const int m0 = m_tile * p.BM;
@@ -300,101 +325,91 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
   } else {
     // =============================== dequantizers ===============================
     // Two groups of four warps take alternate 64-k steps, so that a group has two step times
-    // for the dependent chain wait -> load -> convert -> store -> fence -> arrive of one step.
-    // A step's packed tile is 256 chunks of 16 bytes; thread t of a group converts chunks
-    // t and t + 128.  Chunk c: packed column np_l = c / 4 of the tile, 16-byte chunk
-    // kc = c % 4 of its 64 bytes -> k in [16 kc, 16 kc + 16) of tile rows
-    // na = 16 (np_l / 8) + np_l % 8 and na + 8.  Output: per row two 16-byte units (k 0-7
-    // and 8-15 of the chunk) at unit index 2 kc and 2 kc + 1, XOR-swizzled with row % 8.
-    const int dt = threadIdx.x - 32 * (2 + kNumEpiWarps);
-    const int group = dt >> 7, t = dt & 127;
+    // for the dependent chain wait -> load -> convert -> tcgen05.st -> arrive of one step.
+    // A warp may only touch the TMEM lanes of its quarter (warp id % 4), and lane = row of the
+    // MMA's first operand = weight column n of the tile: thread <-> n = 32 (warp % 4) + lane.
+    // Column n lives in packed column np_l = 8 (n / 16) + n % 8 of the tile, in the "low"
+    // nibble positions when n % 16 < 8 and 8 bits further up otherwise (the thread of n +- 8
+    // reads the same bytes).  Per step it reads the column's 64 bytes and writes 32 TMEM
+    // columns: column j = fp16 pair k = (2j, 2j + 1).
+    const int dw = warp - (2 + kNumEpiWarps);
+    const int group = dw / kWarpsPerDeqGroup;
+    const int n_l = 32 * (warp & 3) + lane;
+    const int np_l = 8 * (n_l >> 4) + (n_l & 7);
+    const uint32_t nib_shift = (n_l & 8) ? 8u : 0u;
+    const uint32_t tmem_row = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)p.a_col0;
     int my_tiles = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) ++my_tiles;
     const uint32_t total_its = (uint32_t)my_tiles * (uint32_t)k_steps;
     for (uint32_t it = group; it < total_its; it += kDeqGroups) {
-      const int s = it % kStages, d = it % kDeqStages;
-      if (!mbar_wait(bar(BAR_FULL + s), (it / kStages) & 1, abort_flag, 0x400 | s)) break;
-      if (it >= (uint32_t)kDeqStages &&
-          !mbar_wait(bar(BAR_DEQ_EMPTY + d), ((it / kDeqStages) - 1) & 1, abort_flag, 0x410 | d))
+      const int s = it % kStages;
+      if (it >= (uint32_t)kStages &&
+          !mbar_wait(bar(BAR_MMA_DONE + s), ((it / kStages) - 1) & 1, abort_flag, 0x410 | s))
         break;
-      const uint8_t* pk = base_ptr + plan.pack + s * kPackTileBytes;
+      if (!mbar_wait(bar(BAR_FULL + s), (it / kStages) & 1, abort_flag, 0x400 | s)) break;
+      tc_fence_after();
+      const uint8_t* pk = base_ptr + plan.pack + s * kPackTileBytes + np_l * 64;
       const uint8_t* sc_tile = base_ptr + plan.scale + s * kScaleTileBytes;
       const uint8_t* zp_tile = base_ptr + plan.zp + s * kZpTileBytes;
-      uint8_t* dq = base_ptr + plan.deq + d * kDeqTileBytes;
+      uint32_t out[32];
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int c = t + 128 * half;
-        const int np_l = c >> 2, kc = c & 3;
-        const int na = 16 * (np_l >> 3) + (np_l & 7), nb = na + 8;
+      for (int c = 0; c < 4; ++c) {  // 16-byte chunk: k in [16 c, 16 c + 16)
         const uint4 wv = *reinterpret_cast<const uint4*>(pk + c * 16);
-        const uint32_t w4[4] = {wv.x, wv.y, wv.z, wv.w};
-
-        uint32_t s_lo_a[4], s_hi_a[4], o_lo_a[4], o_hi_a[4];
-        uint32_t s_lo_b[4], s_hi_b[4], o_lo_b[4], o_hi_b[4];
+        const uint32_t w4[4] = {wv.x >> nib_shift, wv.y >> nib_shift, wv.z >> nib_shift, wv.w >> nib_shift};
+        // scale / offset half2 for the k pairs (2r, 2r+1) [lo] and (2r+8, 2r+9) [hi] of word r
+        uint32_t s_lo[4], s_hi[4], o_lo[4], o_hi[4];
         if (COLWISE) {
-          // scale tile: meta_rows x 128 fp16; row of this chunk within the step
-          const int mr = (p.block >= BLOCK_K) ? 0 : (kc * 16) / p.block;
-          const __half* sp = reinterpret_cast<const __half*>(sc_tile) + mr * TILE_N;
-          const __half sa = sp[na], sb = sp[nb];
-          int za = 8, zb = 8;
-          if (p.has_zp) {
-            za = zp_tile[mr * TILE_N + na];
-            zb = zp_tile[mr * TILE_N + nb];
-          }
-          const __half oa = dequant_offset(sa, za), ob = dequant_offset(sb, zb);
-          const uint32_t sa2 = pack_half2(sa, sa), sb2 = pack_half2(sb, sb);
-          const uint32_t oa2 = pack_half2(oa, oa), ob2 = pack_half2(ob, ob);
+          // scale tile: meta_rows x 128 fp16; the 16 k of a chunk share one block
+          const int mr = (p.block >= BLOCK_K) ? 0 : (c * 16) / p.block;
+          const __half sc = reinterpret_cast<const __half*>(sc_tile)[mr * TILE_N + n_l];
+          const int z = p.has_zp ? (int)zp_tile[mr * TILE_N + n_l] : 8;
+          const __half of = dequant_offset(sc, z);
+          const uint32_t sc2 = pack_half2(sc, sc), of2 = pack_half2(of, of);
 #pragma unroll
           for (int r = 0; r < 4; ++r) {
-            s_lo_a[r] = s_hi_a[r] = sa2;
-            o_lo_a[r] = o_hi_a[r] = oa2;
-            s_lo_b[r] = s_hi_b[r] = sb2;
-            o_lo_b[r] = o_hi_b[r] = ob2;
+            s_lo[r] = s_hi[r] = sc2;
+            o_lo[r] = o_hi[r] = of2;
           }
         } else {
           // scale tile: (128 / block) rows x 64 k fp16, k permuted per 16 as
           // 0 1 8 9 2 3 10 11 ...; zero points 0 8 1 9 2 10 3 11 ...
-          const int mr = na / p.block;
-          const uint4* sp = reinterpret_cast<const uint4*>(sc_tile + mr * 128 + kc * 32);
+          const int mr = n_l / p.block;
+          const uint4* sp = reinterpret_cast<const uint4*>(sc_tile + mr * 128 + c * 32);
           const uint4 s0 = sp[0], s1 = sp[1];
           const uint32_t sw[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
           uint4 zv = make_uint4(0x08080808u, 0x08080808u, 0x08080808u, 0x08080808u);
-          if (p.has_zp) zv = *reinterpret_cast<const uint4*>(zp_tile + mr * 64 + kc * 16);
+          if (p.has_zp) zv = *reinterpret_cast<const uint4*>(zp_tile + mr * 64 + c * 16);
           const uint32_t zw[4] = {zv.x, zv.y, zv.z, zv.w};
 #pragma unroll
           for (int r = 0; r < 4; ++r) {
-            s_lo_a[r] = s_lo_b[r] = sw[2 * r];
-            s_hi_a[r] = s_hi_b[r] = sw[2 * r + 1];
+            s_lo[r] = sw[2 * r];
+            s_hi[r] = sw[2 * r + 1];
             const uint32_t nz_lo = ((zw[r] << 6) & 0x03c003c0u) | 0xcc00cc00u;  // fp16(-16 - z)
             const uint32_t nz_hi = ((zw[r] >> 2) & 0x03c003c0u) | 0xcc00cc00u;
-            o_lo_a[r] = o_lo_b[r] = hmul2_u32(sw[2 * r], nz_lo);
-            o_hi_a[r] = o_hi_b[r] = hmul2_u32(sw[2 * r + 1], nz_hi);
+            o_lo[r] = hmul2_u32(sw[2 * r], nz_lo);
+            o_hi[r] = hmul2_u32(sw[2 * r + 1], nz_hi);
           }
         }
-
-        // word r -> k pairs (2r, 2r+1) and (2r+8, 2r+9) of both rows
-        uint32_t a_lo[4], a_hi[4], b_lo[4], b_hi[4];
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
-          uint32_t h[4];
-          word_to_half16plus(w4[r], h);
-          a_lo[r] = hfma2_u32(s_lo_a[r], h[0], o_lo_a[r]);
-          a_hi[r] = hfma2_u32(s_hi_a[r], h[1], o_hi_a[r]);
-          b_lo[r] = hfma2_u32(s_lo_b[r], h[2], o_lo_b[r]);
-          b_hi[r] = hfma2_u32(s_hi_b[r], h[3], o_hi_b[r]);
+          // after the shift this thread's nibbles sit where column n0's do: bits 0-3 / 16-19 hold
+          // k = 2r, 2r+1 and bits 4-7 / 20-23 hold k = 2r+8, 2r+9; fp16(16 + q) by bit placement
+          const uint32_t h_lo = ((w4[r] << 6) & 0x03c003c0u) | 0x4c004c00u;
+          const uint32_t h_hi = ((w4[r] << 2) & 0x03c003c0u) | 0x4c004c00u;
+          const uint32_t d_lo = hfma2_u32(s_lo[r], h_lo, o_lo[r]);
+          const uint32_t d_hi = hfma2_u32(s_hi[r], h_hi, o_hi[r]);
+          // chunk c, word r: k = 16 c + 2 r (+1) -> column 8 c + r; k + 8 -> column 8 c + 4 + r
+          out[8 * c + r] = d_lo;
+          out[8 * c + 4 + r] = d_hi;
         }
-        const uint32_t row_a = (uint32_t)na * 128u, row_b = (uint32_t)nb * 128u;
-        const uint32_t sw_a = (uint32_t)(na & 7), sw_b = (uint32_t)(nb & 7);
-        *reinterpret_cast<uint4*>(dq + row_a + (((2 * kc) ^ sw_a) << 4)) = make_uint4(a_lo[0], a_lo[1], a_lo[2], a_lo[3]);
-        *reinterpret_cast<uint4*>(dq + row_a + (((2 * kc + 1) ^ sw_a) << 4)) = make_uint4(a_hi[0], a_hi[1], a_hi[2], a_hi[3]);
-        *reinterpret_cast<uint4*>(dq + row_b + (((2 * kc) ^ sw_b) << 4)) = make_uint4(b_lo[0], b_lo[1], b_lo[2], b_lo[3]);
-        *reinterpret_cast<uint4*>(dq + row_b + (((2 * kc + 1) ^ sw_b) << 4)) = make_uint4(b_hi[0], b_hi[1], b_hi[2], b_hi[3]);
       }
-      fence_proxy_async();  // generic-proxy writes -> visible to the tensor core (async proxy)
+      tmem_st_32x32b_x32(tmem_row + (uint32_t)(s * kDeqCols), out);
+      tmem_st_wait();
+      tc_fence_before();
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(bar(BAR_DEQ_FULL + d));
-        mbar_arrive(bar(BAR_EMPTY + s));
+        mbar_arrive(bar(BAR_DEQ_FULL + s));
+        mbar_arrive(bar(BAR_PACK_FREE + s));
       }
     }
   }
@@ -425,6 +440,14 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
   p.n_tiles = (N + TILE_N - 1) / TILE_N;
   p.has_zp = zp != nullptr;
   p.out = out;
+  // tensor memory: accumulators first, then the dequantized stages
+  p.acc_bufs = (2 * p.BM + kDeqStages * kDeqCols <= 512) ? 2 : 1;
+  p.a_col0 = p.acc_bufs * p.BM;
+  {
+    const uint32_t need = (uint32_t)(p.a_col0 + kDeqStages * kDeqCols);
+    p.tmem_cols = 32;
+    while (p.tmem_cols < need) p.tmem_cols <<= 1;
+  }
 
   CUtensorMap tm_act, tm_pack, tm_scale, tm_zp;
   bool ok = encode_tensor_map_2d(&tm_act, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a, (uint64_t)K, (uint64_t)M, BLOCK_K,
