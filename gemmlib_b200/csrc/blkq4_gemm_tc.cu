@@ -14,8 +14,9 @@
 // re-read per step, on top of the TMA traffic, cost a third of the step time.
 //
 // Persistent CTAs (one per SM) walk the tile list.  Warp roles:
-//   warp 0      TMA producer: per 64-k step one activation tile (128-byte swizzle),
-//               one 64 x 64-byte tile of packed int4 weights, its scales and zero points
+//   warp 0      TMA producer of the activation tiles (128-byte swizzle), five stages
+//   warp 14     TMA producer of the packed int4 weight tiles (64 x 64 bytes per 64-k step),
+//               their scales and zero points, eight stages
 //   warp 1      MMA issuer (one elected lane); owns the TMEM allocation
 //   warps 2-5   epilogue: tcgen05.ld -> fp16 -> global, overlapped with the next tile
 //               through a second TMEM accumulator buffer
@@ -42,14 +43,26 @@ namespace {
 constexpr int TILE_N = 128;       // weight columns per tile (UMMA M)
 constexpr int BLOCK_K = 64;       // k per pipeline step: one 128-byte swizzle row of fp16
 constexpr int UMMA_K = 16;
-constexpr int kStages = 5;        // TMA ring (shared memory) = dequantized-weight ring (tensor memory)
-constexpr int kDeqStages = kStages;
+// Two rings.  The weight path (TMA -> shared memory -> dequantize -> tensor memory -> MMA) has a
+// loop latency of several step times, so it is eight stages deep; its stages are small (5.5 KB of
+// shared memory, 32 TMEM columns).  The activation path (TMA -> shared memory -> MMA) is short
+// but its stages are 32 KB, so it gets six.
+constexpr int kActStages = 6;
+constexpr int kStages = 6;        // weight ring in shared memory: packed tile + scales + zero points
+constexpr int kDeqStages = 8;     // dequantized weights in tensor memory
+// tcgen05.commit costs about as much pipe time as one 128x256x16 MMA (measured: 128 cycles per MMA
+// back to back, 241 with a commit after each), so completion is signalled once per kCommitSteps
+// k steps and both rings are released at that granularity.
+constexpr int kCommitSteps = 1;
+constexpr int kDoneBars = kDeqStages / kCommitSteps;
+static_assert(kActStages % kCommitSteps == 0 && kDeqStages % kCommitSteps == 0, "rings are released per commit group");
 constexpr int kDeqCols = BLOCK_K / 2;  // TMEM columns of one dequantized stage: 2 fp16 per column
 constexpr int kNumDeqWarps = 8;
 constexpr int kDeqGroups = 2;     // warp groups taking alternate k steps
 constexpr int kWarpsPerDeqGroup = kNumDeqWarps / kDeqGroups;
 constexpr int kNumEpiWarps = 4;
-constexpr int kThreads = 32 * (2 + kNumEpiWarps + kNumDeqWarps);
+constexpr int kWeightProducerWarp = 2 + kNumEpiWarps + kNumDeqWarps;  // last warp
+constexpr int kThreads = 32 * (3 + kNumEpiWarps + kNumDeqWarps);
 constexpr int kPackTileBytes = (TILE_N / 2) * BLOCK_K;  // 4 KB: 64 packed columns x 64 bytes
 constexpr int kScaleTileBytes = 1024;
 constexpr int kZpTileBytes = 512;
@@ -88,6 +101,24 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The four MMAs of one 64-k step: operand A advances 8 TMEM columns, operand B two
+// descriptor units (32 bytes) per 16 k.  Only the first may overwrite the accumulator.
+__device__ __forceinline__ void umma_f16_ts_x4(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 b0, b1, b2, b3;\n\t.reg .b32 l1, l2, l3, a1, a2, a3;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "setp.eq.b32 q, 0, 0;\n\t"
+      "add.u32 l1, %2, 2;\n\tadd.u32 l2, %2, 4;\n\tadd.u32 l3, %2, 6;\n\t"
+      "add.u32 a1, %1, 8;\n\tadd.u32 a2, %1, 16;\n\tadd.u32 a3, %1, 24;\n\t"
+      "mov.b64 b0, {%2, %3};\n\tmov.b64 b1, {l1, %3};\n\tmov.b64 b2, {l2, %3};\n\tmov.b64 b3, {l3, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], b0, %4, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], b1, %4, q;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], b2, %4, q;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], b3, %4, q;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -150,11 +181,11 @@ __host__ __device__ inline SmemPlan make_plan(int BM) {
   SmemPlan p;
   p.act_bytes = (uint32_t)BM * 128u;
   uint32_t o = 0;
-  p.act = o;   o += kStages * ((p.act_bytes + 1023u) & ~1023u);     // 1024-aligned tiles
+  p.act = o;   o += kActStages * ((p.act_bytes + 1023u) & ~1023u);  // 1024-aligned tiles
   p.pack = o;  o += kStages * kPackTileBytes;
   p.scale = o; o += kStages * kScaleTileBytes;
   p.zp = o;    o += kStages * kZpTileBytes;
-  p.bars = o;  o += 256;
+  p.bars = o;  o += 512;
   p.total = o + 1024;  // slack to align the dynamic base to 1024
   return p;
 }
@@ -162,15 +193,16 @@ __host__ __device__ inline SmemPlan make_plan(int BM) {
 // Barrier slots (8 bytes each) inside the barrier block.  Stage s of the TMA ring and stage s
 // of the dequantized ring belong to the same k step, so one "MMA done" barrier frees both.
 enum : int {
-  BAR_FULL = 0,                           // [kStages] TMA data landed (producer -> dequantizers)
+  BAR_ACT_FULL = 0,                       // [kActStages] activation tile landed (-> MMA issuer)
+  BAR_FULL = BAR_ACT_FULL + kActStages,   // [kStages] packed weights + meta landed (-> dequantizers)
   BAR_PACK_FREE = BAR_FULL + kStages,     // [kStages] packed weights / meta read (dequantizers -> producer)
-  BAR_DEQ_FULL = BAR_PACK_FREE + kStages, // [kStages] dequantized stage written to TMEM (-> MMA issuer)
-  BAR_MMA_DONE = BAR_DEQ_FULL + kStages,  // [kStages] the step's MMAs retired (-> producer, dequantizers)
-  BAR_ACC_FULL = BAR_MMA_DONE + kStages,  // [2] accumulator complete
+  BAR_DEQ_FULL = BAR_PACK_FREE + kStages, // [kDeqStages] dequantized stage written to TMEM (-> MMA issuer)
+  BAR_MMA_DONE = BAR_DEQ_FULL + kDeqStages,  // [kDoneBars] MMAs of commit group g = it / kCommitSteps retired, index g % kDoneBars
+  BAR_ACC_FULL = BAR_MMA_DONE + kDoneBars,  // [2] accumulator complete
   BAR_ACC_EMPTY = BAR_ACC_FULL + 2,       // [2] accumulator drained by the epilogue
   BAR_COUNT = BAR_ACC_EMPTY + 2
 };
-static_assert(BAR_COUNT * 8 + 16 <= 256, "barrier block too small");
+static_assert(BAR_COUNT * 8 + 16 <= 512, "barrier block too small");
 
 template <bool COLWISE>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -193,12 +225,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
   const uint32_t tmem_cols = p.tmem_cols;
 
   if (threadIdx.x == 0) {
+    for (int i = 0; i < kActStages; ++i) mbar_init(bar(BAR_ACT_FULL + i), 1);
     for (int i = 0; i < kStages; ++i) {
       mbar_init(bar(BAR_FULL + i), 1);
       mbar_init(bar(BAR_PACK_FREE + i), kWarpsPerDeqGroup);
-      mbar_init(bar(BAR_DEQ_FULL + i), kWarpsPerDeqGroup);
-      mbar_init(bar(BAR_MMA_DONE + i), 1);
     }
+    for (int i = 0; i < kDeqStages; ++i) mbar_init(bar(BAR_DEQ_FULL + i), kWarpsPerDeqGroup);
+    for (int i = 0; i < kDoneBars; ++i) mbar_init(bar(BAR_MMA_DONE + i), 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(BAR_ACC_FULL + i), 1);
       mbar_init(bar(BAR_ACC_EMPTY + i), kNumEpiWarps);
@@ -219,23 +252,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // =============================== TMA producer ===============================
+    // ========================= TMA producer: activations ========================
+    // Stage sa = it % kActStages is free once the commit group of step it - kActStages retired.
     if (lane == 0) {
-      const uint32_t tx = plan.act_bytes + kPackTileBytes + (uint32_t)p.meta_rows * p.meta_row_bytes_s +
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        const int m_tile = tile % p.m_tiles;
+        for (int ks = 0; ks < k_steps; ++ks, ++it) {
+          const int sa = it % kActStages;
+          if (it >= (uint32_t)kActStages) {
+            const uint32_t g = (it - kActStages) / kCommitSteps;  // commit group of the stage's last user
+            if (!mbar_wait(bar(BAR_MMA_DONE + g % kDoneBars), (g / kDoneBars) & 1, abort_flag, 0x100 | sa))
+              goto act_producer_done;
+          }
+          const uint32_t fb = bar(BAR_ACT_FULL + sa);
+          mbar_arrive_expect_tx(fb, plan.act_bytes);
+          tma_load_2d(base + plan.act + sa * act_stride, &tm_act, ks * BLOCK_K, m_tile * p.BM, fb);
+        }
+      }
+    act_producer_done:;
+    }
+  } else if (warp == kWeightProducerWarp) {
+    // ==================== TMA producer: packed weights and meta =================
+    if (lane == 0) {
+      const uint32_t tx = kPackTileBytes + (uint32_t)p.meta_rows * p.meta_row_bytes_s +
                           (p.has_zp ? (uint32_t)p.meta_rows * p.meta_row_bytes_z : 0u);
       uint32_t it = 0;
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-        const int n_tile = tile / p.m_tiles, m_tile = tile % p.m_tiles;
+        const int n_tile = tile / p.m_tiles;
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
           const int s = it % kStages;
           if (it >= (uint32_t)kStages &&
-              (!mbar_wait(bar(BAR_MMA_DONE + s), ((it / kStages) - 1) & 1, abort_flag, 0x100 | s) ||
-               !mbar_wait(bar(BAR_PACK_FREE + s), ((it / kStages) - 1) & 1, abort_flag, 0x110 | s)))
-            goto producer_done;
+              !mbar_wait(bar(BAR_PACK_FREE + s), ((it / kStages) - 1) & 1, abort_flag, 0x110 | s))
+            goto w_producer_done;
           const uint32_t fb = bar(BAR_FULL + s);
           mbar_arrive_expect_tx(fb, tx);
           const int k0 = ks * BLOCK_K;
-          tma_load_2d(base + plan.act + s * act_stride, &tm_act, k0, m_tile * p.BM, fb);
           tma_load_2d(base + plan.pack + s * kPackTileBytes, &tm_pack, k0, n_tile * (TILE_N / 2), fb);
           if (COLWISE) {
             // meta row-major [K/block, N]: box = meta_rows x 128 columns
@@ -251,43 +303,48 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
           }
         }
       }
-    producer_done:;
+    w_producer_done:;
     }
   } else if (warp == 1) {
     // =============================== MMA issuer =================================
+    // One thread drives the tensor pipe, and its own instruction stream is the critical
+    // path of the kernel: a 128x256x16 MMA takes 128 cycles, so the waits, address
+    // arithmetic, four issues and the commit of a 64-k step must fit in 512 cycles of
+    // dependent scalar code.  Hence: ring indices and parities are carried incrementally
+    // (no division), the four MMAs of a step are one asm block, and the barrier polls take
+    // the slow (bounded, instrumented) path only when the first poll fails.
     if (lane == 0) {
       const uint32_t idesc = make_idesc_f16(TILE_N, p.BM);
-      uint32_t it = 0, tcount = 0;
+      const uint32_t desc_hi = (uint32_t)(make_sw128_kmajor_desc(0) >> 32);
+      const uint32_t desc_lo_flags = (uint32_t)(make_sw128_kmajor_desc(0) & 0xFFFFFFFFu);  // LBO field
+      const uint32_t act_lo0 = desc_lo_flags | (((base + plan.act) >> 4) & 0x3FFFu);
+      const uint32_t act_lo_step = act_stride >> 4;
+      const uint32_t a_tmem0 = tmem_base + (uint32_t)p.a_col0;
+      uint32_t s = 0, sa = 0, par_s = 0, par_sa = 0, gdone = 0, it = 0, tcount = 0;
+      uint32_t ab = 0, par_acc = 0;
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
-        const int ab = tcount % p.acc_bufs;
         if (tcount >= (uint32_t)p.acc_bufs &&
-            !mbar_wait(bar(BAR_ACC_EMPTY + ab), ((tcount / p.acc_bufs) - 1) & 1, abort_flag, 0x200 | ab))
+            !mbar_wait(bar(BAR_ACC_EMPTY + ab), par_acc ^ 1u, abort_flag, 0x200 | ab))
           goto mma_done;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(ab * p.BM);
+        const uint32_t d_tmem = tmem_base + ab * (uint32_t)p.BM;
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
-          const int s = it % kStages;
-          // The dequantizers waited for the step's TMA data before writing TMEM, so this one
-          // wait also covers the activation tile.  The issuing thread is the serial bottleneck
-          // of the pipeline (one wait, four MMAs, one commit per step must fit in the ~540
-          // cycles the MMAs take), hence a single barrier in and a single commit out.
-          if (!mbar_wait(bar(BAR_DEQ_FULL + s), (it / kStages) & 1, abort_flag, 0x220 | s)) goto mma_done;
+          const uint32_t bar_a = bar(BAR_ACT_FULL) + 8u * sa, bar_d = bar(BAR_DEQ_FULL) + 8u * s;
+          if (!mbar_try_wait(bar_a, par_sa) && !mbar_wait(bar_a, par_sa, abort_flag, 0x210 | sa)) goto mma_done;
+          if (!mbar_try_wait(bar_d, par_s) && !mbar_wait(bar_d, par_s, abort_flag, 0x220 | s)) goto mma_done;
           tc_fence_after();
-          const uint32_t a_tmem = tmem_base + (uint32_t)(p.a_col0 + s * kDeqCols);
-          const uint64_t b_desc = make_sw128_kmajor_desc(base + plan.act + s * act_stride);
-          if (ks == 0) {
-            umma_f16_ts(d_tmem, a_tmem, b_desc, idesc, 0u);
-          } else {
-            umma_f16_ts(d_tmem, a_tmem, b_desc, idesc, 1u);
+          // 16 k = 8 TMEM columns of the weights, 32 bytes (2 descriptor units) of the activation row
+          umma_f16_ts_x4(d_tmem, a_tmem0 + s * kDeqCols, act_lo0 + sa * act_lo_step, desc_hi, idesc,
+                         ks > 0 ? 1u : 0u);
+          if (it % kCommitSteps == kCommitSteps - 1) {
+            umma_commit(bar(BAR_MMA_DONE) + 8u * gdone);
+            if (++gdone == kDoneBars) gdone = 0;
           }
-#pragma unroll
-          for (int k = 1; k < BLOCK_K / UMMA_K; ++k) {
-            // 16 k = 8 TMEM columns of the weights, 32 bytes (2 descriptor units) of the activation row
-            umma_f16_ts(d_tmem, a_tmem + k * (UMMA_K / 2), b_desc + (uint64_t)(2 * k), idesc, 1u);
-          }
-          umma_commit(bar(BAR_MMA_DONE + s));
+          if (++s == kDeqStages) { s = 0; par_s ^= 1u; }
+          if (++sa == kActStages) { sa = 0; par_sa ^= 1u; }
         }
         umma_commit(bar(BAR_ACC_FULL + ab));
+        if (++ab == (uint32_t)p.acc_bufs) { ab = 0; par_acc ^= 1u; }
       }
     mma_done:;
     }
@@ -322,7 +379,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(BAR_ACC_EMPTY + ab));
     }
-  } else {
+  } else if (warp < kWeightProducerWarp) {
     // =============================== dequantizers ===============================
     // Two groups of four warps take alternate 64-k steps, so that a group has two step times
     // for the dependent chain wait -> load -> convert -> tcgen05.st -> arrive of one step.
@@ -342,10 +399,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) ++my_tiles;
     const uint32_t total_its = (uint32_t)my_tiles * (uint32_t)k_steps;
     for (uint32_t it = group; it < total_its; it += kDeqGroups) {
-      const int s = it % kStages;
-      if (it >= (uint32_t)kStages &&
-          !mbar_wait(bar(BAR_MMA_DONE + s), ((it / kStages) - 1) & 1, abort_flag, 0x410 | s))
-        break;
+      const int s = it % kStages, d = it % kDeqStages;
+      if (it >= (uint32_t)kDeqStages) {
+        const uint32_t g = (it - kDeqStages) / kCommitSteps;  // commit group of the TMEM stage's last user
+        if (!mbar_wait(bar(BAR_MMA_DONE + g % kDoneBars), (g / kDoneBars) & 1, abort_flag, 0x410 | d)) break;
+      }
       if (!mbar_wait(bar(BAR_FULL + s), (it / kStages) & 1, abort_flag, 0x400 | s)) break;
       tc_fence_after();
       const uint8_t* pk = base_ptr + plan.pack + s * kPackTileBytes + np_l * 64;
@@ -403,12 +461,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
           out[8 * c + 4 + r] = d_hi;
         }
       }
-      tmem_st_32x32b_x32(tmem_row + (uint32_t)(s * kDeqCols), out);
+      tmem_st_32x32b_x32(tmem_row + (uint32_t)(d * kDeqCols), out);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(bar(BAR_DEQ_FULL + s));
+        mbar_arrive(bar(BAR_DEQ_FULL + d));
         mbar_arrive(bar(BAR_PACK_FREE + s));
       }
     }
