@@ -362,17 +362,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       tc_fence_after();
       const int n = n_tile * TILE_N + quarter * 32 + lane;
       const int m0 = m_tile * p.BM;
+      // Lanes pair up (n even / odd) so that every store carries two adjacent n (4 bytes per
+      // lane, 128 contiguous bytes per warp): the even lane writes the even rows m of a
+      // 32-row chunk, the odd lane the odd rows, each with its partner's value alongside.
+      const int odd = lane & 1;
+      const bool n_ok = (n | 1) < p.N;  // N is a multiple of 16: the pair is in or out together
       for (int c0 = 0; c0 < p.BM; c0 += 32) {
         if (m0 + c0 >= p.M) break;  // warp-uniform
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(ab * p.BM + c0), r);
         tmem_ld_wait();
-        if (n < p.N) {
+        int m = m0 + c0 + odd;
+        __half* dst = p.out + (size_t)m * p.N + (n & ~1);
+        const size_t row_step = 2 * (size_t)p.N;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int m = m0 + c0 + j;
-            if (m < p.M) p.out[(size_t)m * p.N + n] = __float2half_rn(__uint_as_float(r[j]));
-          }
+        for (int j = 0; j < 32; j += 2) {
+          const float mine = __uint_as_float(odd ? r[j + 1] : r[j]);       // my n, my row
+          const float give = __uint_as_float(odd ? r[j] : r[j + 1]);       // my n, partner's row
+          const float got = __shfl_xor_sync(0xffffffffu, give, 1);          // partner's n, my row
+          const __half2 v = odd ? __floats2half2_rn(got, mine) : __floats2half2_rn(mine, got);
+          if (n_ok && m < p.M) *reinterpret_cast<__half2*>(dst) = v;
+          dst += row_step;
+          m += 2;
         }
       }
       tc_fence_before();
