@@ -70,6 +70,7 @@ constexpr long long kWaitCycles = 4000000000ll;  // ~2 s: far beyond any legitim
 
 struct Params {
   int M, N, K, block;
+  int block_shift;   // log2(block)
   int BM;            // activation rows per tile = UMMA N (multiple of 16, <= 256)
   int m_tiles, n_tiles;
   int has_zp;
@@ -429,11 +430,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         uint32_t s_lo[4], s_hi[4], o_lo[4], o_hi[4];
         if (COLWISE) {
           // scale tile: meta_rows x 128 fp16; the 16 k of a chunk share one block
-          const int mr = (p.block >= BLOCK_K) ? 0 : (c * 16) / p.block;
-          const __half sc = reinterpret_cast<const __half*>(sc_tile)[mr * TILE_N + n_l];
-          const int z = p.has_zp ? (int)zp_tile[mr * TILE_N + n_l] : 8;
-          const __half of = dequant_offset(sc, z);
-          const uint32_t sc2 = pack_half2(sc, sc), of2 = pack_half2(of, of);
+          const int mr = (p.block >= BLOCK_K) ? 0 : ((c * 16) >> p.block_shift);
+          const uint32_t sc = reinterpret_cast<const unsigned short*>(sc_tile)[mr * TILE_N + n_l];
+          const uint32_t z = p.has_zp ? (uint32_t)zp_tile[mr * TILE_N + n_l] : 8u;
+          const uint32_t sc2 = sc | (sc << 16);
+          // fp16(-16 - z) by bit placement (0xcc00 is -16.0, mantissa step 1/64), times the scale
+          const uint32_t nz = 0xcc00u | (z << 6);
+          const uint32_t of2 = hmul2_u32(sc2, nz | (nz << 16));
 #pragma unroll
           for (int r = 0; r < 4; ++r) {
             s_lo[r] = s_hi[r] = sc2;
@@ -504,6 +507,7 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
                            const uint8_t* zp, __half* out) {
   Params p{};
   p.M = M; p.N = N; p.K = K; p.block = block;
+  p.block_shift = block == 16 ? 4 : block == 32 ? 5 : block == 64 ? 6 : 7;
   p.BM = M >= 256 ? 256 : ((M + 15) / 16) * 16;
   p.m_tiles = (M + p.BM - 1) / p.BM;
   p.n_tiles = (N + TILE_N - 1) / TILE_N;
