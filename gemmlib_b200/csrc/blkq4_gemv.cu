@@ -534,8 +534,16 @@ gemv_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
         }
 #pragma unroll
         for (int j = 0; j < MT; ++j) {
-          const uint4* ap = reinterpret_cast<const uint4*>(aptr[j] + step * 64);
-          const uint4 v0 = ap[0], v1 = ap[1];  // k 0-7 and 8-15 of this lane's chunk
+          uint4 v0, v1;  // k 0-7 and 8-15 of this lane's chunk
+          if (p.a_smem) {  // explicit shared-memory loads (a generic load would go through L1TEX)
+            const uint32_t sa_addr = smem_u32(aptr[j] + step * 64);
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v0.x), "=r"(v0.y), "=r"(v0.z), "=r"(v0.w) : "r"(sa_addr));
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v1.x), "=r"(v1.y), "=r"(v1.z), "=r"(v1.w) : "r"(sa_addr + 16));
+          } else {
+            const uint4* ap = reinterpret_cast<const uint4*>(aptr[j] + step * 64);
+            v0 = __ldg(ap);
+            v1 = __ldg(ap + 1);
+          }
           float acc[4];
           mma_m16n8k16_init(acc, lo_a[0], lo_b[0], lo_a[1], lo_b[1], v0.x, v0.y);
           mma_m16n8k16(acc, lo_a[2], lo_b[2], lo_a[3], lo_b[3], v0.z, v0.w);

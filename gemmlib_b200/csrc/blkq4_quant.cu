@@ -70,11 +70,14 @@ __device__ __forceinline__ __half range_to_scale(float mn, float mx, float first
 
 // q = clamp(roundf(v * r + zp), 0, 15).  The reference's expression
 // (f16_quant_sm80.cuh:295-296) is compiled by nvcc with its default fused
-// multiply-add contraction; the fma is explicit here.
+// multiply-add contraction; the fma is explicit here.  roundf (halves away from zero)
+// commutes with the clamp because 0 and 15 are integers, and for x in [0, 15] it equals
+// trunc(x + 0.5) when the addition rounds toward zero (the sum can then never be pushed
+// up to the next integer), which is two instructions instead of a library call.
 __device__ __forceinline__ uint32_t quantize_one(float v, float r, float zp) {
-  float x = roundf(__fmaf_rn(v, r, zp));
+  float x = __fmaf_rn(v, r, zp);
   x = fmaxf(0.0f, fminf(15.0f, x));
-  return (uint32_t)x;
+  return (uint32_t)__float2int_rz(__fadd_rz(x, 0.5f));
 }
 
 template <int BLOCK, bool COLWISE>
@@ -126,13 +129,20 @@ quant_prepack_kernel(const __half* __restrict__ w, int K, int N, int ld, bool ve
     float mn = __FLT_MAX__, mx = -__FLT_MAX__;
     if constexpr (COLWISE) {
       const int col = seg / (TK / 16), sk = seg % (TK / 16);
-      const __half* p = &s_w[col * PITCH + sk * 16];
+      const uint4* p = reinterpret_cast<const uint4*>(&s_w[col * PITCH + sk * 16]);
+      const uint4 v0 = p[0], v1 = p[1];
+      const __half2* h0 = reinterpret_cast<const __half2*>(&v0);
+      const __half2* h1 = reinterpret_cast<const __half2*>(&v1);
+      // fp16 min/max are exact; NaNs are skipped as in the reference's "v < min" scan
+      __half2 mn2 = __hmin2(h0[0], h1[0]), mx2 = __hmax2(h0[0], h1[0]);
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float v = __half2float(p[i]);
-        mn = fminf(mn, v);
-        mx = fmaxf(mx, v);
+      for (int i = 1; i < 4; ++i) {
+        mn2 = __hmin2(mn2, __hmin2(h0[i], h1[i]));
+        mx2 = __hmax2(mx2, __hmax2(h0[i], h1[i]));
       }
+      const float2 fmn = __half22float2(mn2), fmx = __half22float2(mx2);
+      mn = fminf(fmn.x, fmn.y);
+      mx = fmaxf(fmx.x, fmx.y);
     } else {
       const int k = seg / (TN / 16), ng = seg % (TN / 16);
 #pragma unroll
