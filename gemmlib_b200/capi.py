@@ -16,6 +16,7 @@ LIB_PATH = os.path.join(_PKG, "libms_blkq4gemm.so")
 
 SYMBOLS = (
     "blkq4_fp16_gemm_sm80",
+    "blkq4_fp16_gemm_sm100",
     "blkq4_fp16_quant_sm80",
     "blkq4_fp16_quant_size_sm80",
     "blkq4_errmsg_create",
@@ -40,6 +41,8 @@ def _load() -> ctypes.CDLL:
     vp, sz, i, b = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_bool
     lib.blkq4_fp16_gemm_sm80.argtypes = [i, b, i, i, i, vp, vp, sz, vp, sz, vp, sz, vp, sz, vp, sz, vp]
     lib.blkq4_fp16_gemm_sm80.restype = i
+    lib.blkq4_fp16_gemm_sm100.argtypes = [i, b, i, i, i, vp, vp, sz, vp, sz, vp, sz, vp, sz, vp, sz, ctypes.c_uint, vp]
+    lib.blkq4_fp16_gemm_sm100.restype = i
     lib.blkq4_fp16_quant_sm80.argtypes = [i, b, i, i, i, vp, vp, sz, vp, sz, vp, sz, vp, sz, vp]
     lib.blkq4_fp16_quant_sm80.restype = i
     i64p = ctypes.POINTER(ctypes.c_int64)  # int64_t& is passed as a pointer
@@ -85,7 +88,7 @@ def version() -> str:
 
 
 def last_kernel_status(stream=0) -> int:
-    """Synchronise ``stream`` and return the tensor-core kernel's device status word."""
+    """Synchronise ``stream`` and return the kernels' device status word (0 = no wait expired)."""
     return int(lib.blkq4_last_kernel_status(stream))
 
 
@@ -114,15 +117,24 @@ def quant(block_size, column_wise, rows, columns, ld, weights, q_weights, q_scal
             raise BlkQ4Error(e.text())
 
 
-def gemm(block_size, column_wise, m, n, k, act, q_weights, q_scales, q_zp, out, stream=0):
+EARLY_WEIGHT_FETCH = 1  # BLKQ4_GEMM_EARLY_WEIGHT_FETCH
+
+
+def gemm(block_size, column_wise, m, n, k, act, q_weights, q_scales, q_zp, out, stream=0, flags=0):
+    """``flags == 0`` calls the reference-named entry point, otherwise ``blkq4_fp16_gemm_sm100``."""
     ap, as_ = _ptr_size(act)
     qp, qs = _ptr_size(q_weights)
     sp, ss = _ptr_size(q_scales)
     zp, zs = _ptr_size(q_zp)
     op, os_ = _ptr_size(out)
     with _ErrMsg() as e:
-        rc = lib.blkq4_fp16_gemm_sm80(
-            block_size, column_wise, m, n, k, stream, ap, as_, qp, qs, sp, ss, zp, zs, op, os_, e.p
-        )
+        if flags:
+            rc = lib.blkq4_fp16_gemm_sm100(
+                block_size, column_wise, m, n, k, stream, ap, as_, qp, qs, sp, ss, zp, zs, op, os_, flags, e.p
+            )
+        else:
+            rc = lib.blkq4_fp16_gemm_sm80(
+                block_size, column_wise, m, n, k, stream, ap, as_, qp, qs, sp, ss, zp, zs, op, os_, e.p
+            )
         if rc != 0:
             raise BlkQ4Error(e.text())

@@ -93,12 +93,12 @@ extern "C" int blkq4_fp16_quant_sm80(int block_size, bool column_wise_blocking, 
   return 0;
 }
 
-extern "C" int blkq4_fp16_gemm_sm80(int block_size, bool column_wise_blocking, int m, int n, int k,
-                                    void* stream_ptr, void const* act_ptr, size_t a_size,
-                                    void const* weights_ptr, size_t weights_size,
-                                    void const* scales_ptr, size_t scales_size,
-                                    void const* offsets_ptr, size_t offsets_size, void* output_ptr,
-                                    size_t output_size, void* err) {
+extern "C" int blkq4_fp16_gemm_sm100(int block_size, bool column_wise_blocking, int m, int n, int k,
+                                     void* stream_ptr, void const* act_ptr, size_t a_size,
+                                     void const* weights_ptr, size_t weights_size,
+                                     void const* scales_ptr, size_t scales_size,
+                                     void const* offsets_ptr, size_t offsets_size, void* output_ptr,
+                                     size_t output_size, unsigned flags, void* err) {
   if (!blkq4::supported_block(block_size))
     return fail(err, "Unsupported block size: " + std::to_string(block_size));
   if (m <= 0 || n <= 0 || k <= 0)
@@ -150,10 +150,21 @@ extern "C" int blkq4_fp16_gemm_sm80(int block_size, bool column_wise_blocking, i
   // (src/blkq4_f16_gemm_sm80.cu:343); here it separates the HBM-bound skinny
   // kernel from the tcgen05 tensor-core kernel.
   const std::string e =
-      (m <= 16) ? blkq4::launch_gemv(block_size, column_wise_blocking, m, n, k, stream, a, w, s, z, o)
+      (m <= 16) ? blkq4::launch_gemv(block_size, column_wise_blocking, m, n, k, stream, a, w, s, z, o, flags)
                 : blkq4::launch_gemm_tc(block_size, column_wise_blocking, m, n, k, stream, a, w, s, z, o);
   if (!e.empty()) return fail(err, "Kernel execution failed: " + e);
   return 0;
+}
+
+extern "C" int blkq4_fp16_gemm_sm80(int block_size, bool column_wise_blocking, int m, int n, int k,
+                                    void* stream_ptr, void const* act_ptr, size_t a_size,
+                                    void const* weights_ptr, size_t weights_size,
+                                    void const* scales_ptr, size_t scales_size,
+                                    void const* offsets_ptr, size_t offsets_size, void* output_ptr,
+                                    size_t output_size, void* err) {
+  return blkq4_fp16_gemm_sm100(block_size, column_wise_blocking, m, n, k, stream_ptr, act_ptr, a_size,
+                               weights_ptr, weights_size, scales_ptr, scales_size, offsets_ptr,
+                               offsets_size, output_ptr, output_size, 0u, err);
 }
 
 extern "C" void* blkq4_errmsg_create(void) { return new std::string(); }
@@ -162,6 +173,9 @@ extern "C" char const* blkq4_errmsg_cstr(void* p) {
 }
 extern "C" void blkq4_errmsg_destroy(void* p) { delete reinterpret_cast<std::string*>(p); }
 extern "C" int blkq4_last_kernel_status(void* stream_ptr) {
-  return blkq4::read_gemm_tc_error(reinterpret_cast<cudaStream_t>(stream_ptr));
+  const int tc = blkq4::read_gemm_tc_error(reinterpret_cast<cudaStream_t>(stream_ptr));
+  if (tc != 0) return tc;
+  const int gv = blkq4::read_gemv_error();
+  return gv > 0 ? (0x10000 | gv) : gv;
 }
 extern "C" char const* blkq4_version(void) { return "gemmlib_b200 0.1 sm_100a"; }

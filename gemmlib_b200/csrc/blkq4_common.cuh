@@ -27,7 +27,7 @@ std::string launch_quant_prepack(int block, bool colwise, int K, int N, int ld,
 
 std::string launch_gemv(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
                         const __half* a, const uint8_t* packed, const __half* scales,
-                        const uint8_t* zp, __half* out);
+                        const uint8_t* zp, __half* out, unsigned flags);
 
 std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
                            const __half* a, const uint8_t* packed, const __half* scales,
@@ -36,6 +36,8 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
 // Synchronises `stream` and returns the tensor-core kernel's device error word
 // (0 = every bounded wait completed; -1 = the stream itself reported an error).
 int read_gemm_tc_error(cudaStream_t stream);
+// The skinny kernel's device error word (call after the stream has been synchronised).
+int read_gemv_error();
 
 #ifdef __CUDACC__
 

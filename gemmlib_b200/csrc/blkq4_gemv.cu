@@ -21,9 +21,12 @@
 // then fma.rn.f16(scale, 16 + q, rn(scale * (-16 - zp))); reference
 // src/mickey/cutlass_ext/q4gemm/warp/quantb_meta_mma_tensor_op_tile_iterator.h:69-104
 // and :436-543.  Accumulation is fp32, output one rounding to fp16.
+#include <cstddef>
+#include <cstdint>
 #include <cstdlib>
 
 #include "blkq4_common.cuh"
+#include "ms_blkq4gemm.h"
 #include "blkq4_tma.cuh"
 
 namespace blkq4 {
@@ -355,6 +358,9 @@ gemv_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   const int bs = p.block_shift - 6;          // meta row of a step = step >> bs
   const int meta_rows = kUnitSteps >> bs;    // rows of the scale / zero-point box of a unit
 
+  // Lets the next kernel of the stream start as soon as every CTA of this one is resident (a
+  // no-op unless that kernel was launched with programmatic stream serialization).
+  asm volatile("griddepcontrol.launch_dependents;");
   if (threadIdx.x == 0) {
     for (int i = 0; i < kRing; ++i) {
       mbar_init(bar_full + 8 * i, 1);
@@ -369,6 +375,8 @@ gemv_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
 
   if (warp == kCons) {
     // ================================ producer ================================
+    // Weights, scales and zero points are read here WITHOUT waiting for the preceding kernel of
+    // the stream (the caller vouches for them when it asks for the early start).
     // Issuing a TMA copy blocks the issuing thread for ~100 ns on B200, so up to 32 lanes issue
     // for different units at once.  Lane l owns ring slot l for the whole kernel (units
     // q = l, l + ring, ...): a slot's barriers are then waited on by one thread, one phase at
@@ -394,33 +402,52 @@ gemv_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
     // ================================ consumers ===============================
     const int g = lane >> 2, t = lane & 3;
     const int ctid = threadIdx.x;  // 0 .. kCons*32-1
+    // Activations and the output belong to stream order: wait for the preceding kernel (returns
+    // at once for a plain launch).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // ---- once per CTA: activations into shared memory (small M) and the activation-only
     //      terms of every 64-k step:  lo = sum of a over k % 16 < 8, hi = sum over k % 16 >= 8
     //      symmetric:   corr = 1024 lo + 64 hi + 8 (lo + hi)
     //      zero points: (bias, asum) = (1024 lo + 64 hi, lo + hi)
-    for (int it = ctid; it < total_steps * p.M; it += kCons * 32) {
-      const int m = it % p.M, step = it / p.M;
-      const uint4* src = reinterpret_cast<const uint4*>(p.a + (size_t)m * p.K + step * 64);
-      float lo = 0.0f, hi = 0.0f;
+    //      Four threads share a (row, step): each sums 8 "lo" and 8 "hi" values.
+    {
+      const int total = total_steps * p.M * 4;
+      for (int base = 0; base < total; base += kCons * 32) {
+        const int idx = base + ctid;
+        const bool valid = idx < total;
+        const int pair = idx >> 2, j = idx & 3;
+        const int m = pair % p.M, step = pair / p.M;
+        float lo = 0.0f, hi = 0.0f;
+        if (valid) {
+          const size_t off = (size_t)m * p.K + step * 64 + j * 16;
+          const uint4 v0 = __ldg(reinterpret_cast<const uint4*>(p.a + off));
+          const uint4 v1 = __ldg(reinterpret_cast<const uint4*>(p.a + off) + 1);
+          if (p.a_smem) {
+            *reinterpret_cast<uint4*>(s_a + off) = v0;
+            *(reinterpret_cast<uint4*>(s_a + off) + 1) = v1;
+          }
+          const __half2* h0 = reinterpret_cast<const __half2*>(&v0);
+          const __half2* h1 = reinterpret_cast<const __half2*>(&v1);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const uint4 v = __ldg(src + c);
-        if (p.a_smem) *reinterpret_cast<uint4*>(s_a + (size_t)m * p.K + step * 64 + c * 8) = v;
-        const __half2* h = reinterpret_cast<const __half2*>(&v);
-        float part = 0.0f;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = __half22float2(h[e]);
-          part += f.x + f.y;
+          for (int e = 0; e < 4; ++e) {
+            const float2 f0 = __half22float2(h0[e]), f1 = __half22float2(h1[e]);
+            lo += f0.x + f0.y;
+            hi += f1.x + f1.y;
+          }
         }
-        if (c & 1) hi += part; else lo += part;
-      }
-      const float bias = 1024.0f * lo + 64.0f * hi, asum = lo + hi;
-      if (HAS_ZP) {
-        s_corr[(step * MR + m) * 2] = bias;
-        s_corr[(step * MR + m) * 2 + 1] = asum;
-      } else {
-        s_corr[step * MR + m] = bias + 8.0f * asum;
+        lo += __shfl_xor_sync(0xffffffffu, lo, 1);
+        hi += __shfl_xor_sync(0xffffffffu, hi, 1);
+        lo += __shfl_xor_sync(0xffffffffu, lo, 2);
+        hi += __shfl_xor_sync(0xffffffffu, hi, 2);
+        if (valid && j == 0) {
+          const float bias = 1024.0f * lo + 64.0f * hi, asum = lo + hi;
+          if (HAS_ZP) {
+            s_corr[(step * MR + m) * 2] = bias;
+            s_corr[(step * MR + m) * 2 + 1] = asum;
+          } else {
+            s_corr[step * MR + m] = bias + 8.0f * asum;
+          }
+        }
       }
     }
     asm volatile("bar.sync 1, %0;" ::"n"(kCons * 32) : "memory");  // consumers only
@@ -582,7 +609,7 @@ static int env_int(const char* name) {
 template <int MT, bool HAS_ZP>
 std::string launch_persistent_T(int M, int N, int K, int block, cudaStream_t stream, const __half* a,
                                 const uint8_t* packed, const __half* scales, const uint8_t* zp,
-                                __half* out) {
+                                __half* out, bool early_fetch) {
   PersistParams p{};
   p.a = a; p.out = out; p.M = M; p.N = N; p.K = K;
   p.block_shift = block == 64 ? 6 : 7;
@@ -615,8 +642,20 @@ std::string launch_persistent_T(int M, int N, int K, int block, cudaStream_t str
   auto kern = gemv_persistent_kernel<MT, HAS_ZP>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return std::string(cudaGetErrorString(e));
-  kern<<<grid, kPersistThreads, smem, stream>>>(tm_w, tm_s, tm_z, p);
-  e = cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kPersistThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  // Programmatic stream serialization: this launch's CTAs may start, and its producer warp may
+  // read weights, scales and zero points, while the preceding kernel of the stream drains.
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = early_fetch ? 1 : 0;
+  e = cudaLaunchKernelEx(&cfg, kern, tm_w, tm_s, tm_z, p);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return std::string(cudaGetErrorString(e));
   return std::string();
 }
@@ -639,10 +678,17 @@ cudaError_t launch_T(int warps, int M, int N, int K, int block, cudaStream_t str
 
 }  // namespace
 
+int read_gemv_error() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_gemv_error, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
+
 std::string launch_gemv(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
                         const __half* a, const uint8_t* packed, const __half* scales,
-                        const uint8_t* zp, __half* out) {
+                        const uint8_t* zp, __half* out, unsigned flags) {
   if (M < 1 || M > 16) return "skinny kernel needs 1 <= M <= 16";
+  const bool early = (flags & BLKQ4_GEMM_EARLY_WEIGHT_FETCH) != 0;
   static const int env_warps = env_int("BLKQ4_GEMV_WARPS"), env_u = env_int("BLKQ4_GEMV_U");
   // Warps per CTA = K splits.  Each warp should see at least four 64-k steps.
   const int steps = K / 64;
@@ -657,10 +703,10 @@ std::string launch_gemv(int block, bool colwise, int M, int N, int K, cudaStream
   if (colwise && block >= 64 && !env_generic && K % kUnitKBytes == 0 && K <= 32768 &&
       reinterpret_cast<uintptr_t>(scales) % 16 == 0 && (!zp || reinterpret_cast<uintptr_t>(zp) % 16 == 0)) {
     if (M <= 8)
-      return zp ? launch_persistent_T<1, true>(M, N, K, block, stream, a, packed, scales, zp, out)
-                : launch_persistent_T<1, false>(M, N, K, block, stream, a, packed, scales, zp, out);
-    return zp ? launch_persistent_T<2, true>(M, N, K, block, stream, a, packed, scales, zp, out)
-              : launch_persistent_T<2, false>(M, N, K, block, stream, a, packed, scales, zp, out);
+      return zp ? launch_persistent_T<1, true>(M, N, K, block, stream, a, packed, scales, zp, out, early)
+                : launch_persistent_T<1, false>(M, N, K, block, stream, a, packed, scales, zp, out, early);
+    return zp ? launch_persistent_T<2, true>(M, N, K, block, stream, a, packed, scales, zp, out, early)
+              : launch_persistent_T<2, false>(M, N, K, block, stream, a, packed, scales, zp, out, early);
   }
   // Row-wise blocking carries 48 bytes of meta per chunk in registers, so it fetches
   // fewer steps at a time.

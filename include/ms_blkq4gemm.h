@@ -105,6 +105,31 @@ int blkq4_fp16_quant_size_sm80(
     int64_t& quant_meta_size,
     void* error_message);
 
+/**
+ * blkq4_fp16_gemm_sm80 with a `flags` word; flags = 0 is exactly that call.  No counterpart in
+ * the reference (its signature is reference include/ms_blkq4gemm.h:41-50 plus `flags`).
+ *
+ * BLKQ4_GEMM_EARLY_WEIGHT_FETCH: the caller vouches that weights, scales and offsets are not
+ * written by any work still pending on `stream` (inference weights, quantized once).  The
+ * kernel is then launched with programmatic stream serialization: it may become resident and
+ * fetch weights while the preceding kernel of the stream still runs, which keeps HBM busy
+ * across the launches of a decode stack.  Activations are read, and the output written, only
+ * after the preceding work has completed, so stream order holds for both.  Honoured by the
+ * skinny kernel (M <= 16); ignored elsewhere.
+ */
+#define BLKQ4_GEMM_EARLY_WEIGHT_FETCH 1u
+int blkq4_fp16_gemm_sm100(
+  int block_size,
+  bool column_wise_blocking,
+  int m, int n, int k, void* stream,
+  void const* act_ptr, size_t a_size,
+  void const* weights_ptr, size_t weights_size,
+  void const* scales_ptr, size_t scales_size,
+  void const* offsets_ptr, size_t offsets_size,
+  void* output_ptr, size_t output_size,
+  unsigned flags,
+  void* error_message);
+
 /*
  * Additions with no counterpart in the reference.  The reference reports errors
  * through a std::string*, which only a C++ caller can supply.  These three let
@@ -115,11 +140,11 @@ char const* blkq4_errmsg_cstr(void* errmsg);  /* its c_str(); valid until reused
 void blkq4_errmsg_destroy(void* errmsg);      /* delete                          */
 
 /**
- * Synchronises `stream` and returns the device-side status word of the tensor-core
- * kernel: 0 when every in-kernel wait completed.  Its waits on mbarriers are bounded;
- * one that expires makes the CTA drain and records (role << 8 | barrier) here instead
- * of hanging the GPU.  -1 if the stream itself is in error.  No counterpart in the
- * reference, whose kernels have no such waits.
+ * Synchronises `stream` and returns the device-side status word of the kernels: 0 when
+ * every in-kernel wait completed.  Waits on mbarriers are bounded; one that expires makes
+ * the CTA drain and records (role << 8 | barrier) here instead of hanging the GPU (the
+ * skinny kernel's word is reported with bit 16 set).  -1 if the stream itself is in error.
+ * No counterpart in the reference, whose kernels have no such waits.
  */
 int blkq4_last_kernel_status(void* stream);
 

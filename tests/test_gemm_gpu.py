@@ -21,14 +21,15 @@ def to_cuda(a):
     return None if a is None else torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
-def gpu_gemm(block, colwise, a_mk, N, packed, scales, zp):
+def gpu_gemm(block, colwise, a_mk, N, packed, scales, zp, flags=0):
     from gemmlib_b200 import capi
 
     M, K = a_mk.shape
     a, pw, ps, pz = to_cuda(a_mk), to_cuda(packed), to_cuda(scales), to_cuda(zp)
     out = torch.full((M, N), float("nan"), dtype=torch.float16, device="cuda")
-    capi.gemm(block, colwise, M, N, K, a, pw, ps, pz, out)
+    capi.gemm(block, colwise, M, N, K, a, pw, ps, pz, out, flags=flags)
     torch.cuda.synchronize()
+    assert capi.last_kernel_status() == 0
     return out.cpu().numpy()
 
 
@@ -62,11 +63,11 @@ def test_every_m_class_exact(M):
         assert (bits(got) == bits(want)).all(), (M, block, colwise, has_zp, N, K)
 
 
-def check_gaussian(block, colwise, has_zp, M, N, K, sigma=0.02):
+def check_gaussian(block, colwise, has_zp, M, N, K, sigma=0.02, flags=0):
     w = gaussian_weight(N, K, sigma=sigma, seed=K + N)
     a = gaussian_act(M, K, seed=M).numpy()
     pw, ps, pz = O.quant_prepack(block, colwise, w.numpy(), has_zp)
-    got = gpu_gemm(block, colwise, a, N, pw, ps, pz).astype(np.float64)
+    got = gpu_gemm(block, colwise, a, N, pw, ps, pz, flags=flags).astype(np.float64)
     assert np.isfinite(got).all()
     wdq = O.dequant(block, colwise, K, N, pw, ps, pz)
     want = O.gemm(a, wdq).astype(np.float64)
@@ -91,6 +92,52 @@ def check_gaussian(block, colwise, has_zp, M, N, K, sigma=0.02):
 @pytest.mark.parametrize("M", [1, 5, 16, 48, 512])
 def test_gaussian_tolerance(block, colwise, has_zp, M):
     check_gaussian(block, colwise, has_zp, M, 384, 512)
+
+
+# Shapes that walk the streaming skinny kernel's corners: more tiles than SMs, fewer tiles than
+# SMs, a last chunk of K that is partial (K % 1024 != 0), fewer items per tile than consumer
+# warps (K < 4096), 9..16 rows, the largest meta box (K / block = 256).
+STREAM_CASES = [
+    (64, False, 1, 4736, 1024), (64, True, 3, 2400, 1280), (128, False, 8, 160, 3072),
+    (128, True, 16, 4768, 2048), (64, True, 9, 2432, 5120), (64, False, 2, 1600, 16384),
+]
+
+
+@pytest.mark.parametrize("flags", [0, 1], ids=["plain", "early_fetch"])
+@pytest.mark.parametrize("case", STREAM_CASES, ids=lambda c: "-".join(map(str, c)))
+def test_streaming_skinny_kernel_shapes(case, flags):
+    block, has_zp, M, N, K = case
+    check_gaussian(block, True, has_zp, M, N, K, flags=flags)
+
+
+def test_early_weight_fetch_keeps_stream_order_for_activations():
+    """A chain of layers on one stream, each consuming the previous output.  With
+    BLKQ4_GEMM_EARLY_WEIGHT_FETCH a launch may fetch weights while its predecessor still
+    runs, but must not read activations (or write its output) before the predecessor is
+    done: the chain's result must match the plainly serialized chain."""
+    from gemmlib_b200 import capi
+
+    K = N = 4096
+    layers = []
+    for i in range(6):
+        w = gaussian_weight(N, K, sigma=0.015, seed=100 + i)
+        layers.append(tuple(to_cuda(x) for x in O.quant_prepack(64, True, w.numpy(), False)))
+    a0 = to_cuda(gaussian_act(1, K, seed=3).numpy())
+
+    def chain(flags):
+        bufs = [a0] + [torch.zeros(1, N, dtype=torch.float16, device="cuda") for _ in layers]
+        for _ in range(3):  # repeat: later rounds run with everything warm
+            for i, (pw, ps, pz) in enumerate(layers):
+                capi.gemm(64, True, 1, N, K, bufs[i], pw, ps, pz, bufs[i + 1], flags=flags)
+        torch.cuda.synchronize()
+        assert capi.last_kernel_status() == 0
+        return [b.float().cpu().numpy() for b in bufs[1:]]
+
+    plain, early = chain(0), chain(capi.EARLY_WEIGHT_FETCH)
+    for i, (x, y) in enumerate(zip(plain, early)):
+        assert np.isfinite(y).all()
+        # fp32 partial sums meet in shared memory in arrival order: equal up to fp16 rounding
+        assert np.abs(x - y).max() <= 2.0 ** -8 * max(1.0, np.abs(x).max()), i
 
 
 def test_config_c1_cpu_reference_case():
