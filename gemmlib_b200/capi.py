@@ -41,7 +41,7 @@ def _load() -> ctypes.CDLL:
     vp, sz, i, b = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_bool
     lib.blkq4_fp16_gemm_sm80.argtypes = [i, b, i, i, i, vp, vp, sz, vp, sz, vp, sz, vp, sz, vp, sz, vp]
     lib.blkq4_fp16_gemm_sm80.restype = i
-    lib.blkq4_fp16_gemm_sm100.argtypes = [i, b, i, i, i, vp, vp, sz, vp, sz, vp, sz, vp, sz, vp, sz, ctypes.c_uint, vp]
+    lib.blkq4_fp16_gemm_sm100.argtypes = [i, b, i, i, i, vp, vp, sz, vp, sz, vp, sz, vp, sz, vp, sz, vp, sz, ctypes.c_uint, vp]
     lib.blkq4_fp16_gemm_sm100.restype = i
     lib.blkq4_fp16_quant_sm80.argtypes = [i, b, i, i, i, vp, vp, sz, vp, sz, vp, sz, vp, sz, vp]
     lib.blkq4_fp16_quant_sm80.restype = i
@@ -120,17 +120,19 @@ def quant(block_size, column_wise, rows, columns, ld, weights, q_weights, q_scal
 EARLY_WEIGHT_FETCH = 1  # BLKQ4_GEMM_EARLY_WEIGHT_FETCH
 
 
-def gemm(block_size, column_wise, m, n, k, act, q_weights, q_scales, q_zp, out, stream=0, flags=0):
-    """``flags == 0`` calls the reference-named entry point, otherwise ``blkq4_fp16_gemm_sm100``."""
+def gemm(block_size, column_wise, m, n, k, act, q_weights, q_scales, q_zp, out, stream=0, flags=0, bias=None):
+    """Without ``flags`` and ``bias`` calls the reference-named entry point, otherwise
+    ``blkq4_fp16_gemm_sm100``."""
     ap, as_ = _ptr_size(act)
     qp, qs = _ptr_size(q_weights)
     sp, ss = _ptr_size(q_scales)
     zp, zs = _ptr_size(q_zp)
     op, os_ = _ptr_size(out)
+    bp, bs = _ptr_size(bias)
     with _ErrMsg() as e:
-        if flags:
+        if flags or bs:
             rc = lib.blkq4_fp16_gemm_sm100(
-                block_size, column_wise, m, n, k, stream, ap, as_, qp, qs, sp, ss, zp, zs, op, os_, flags, e.p
+                block_size, column_wise, m, n, k, stream, ap, as_, qp, qs, sp, ss, zp, zs, op, os_, bp, bs, flags, e.p
             )
         else:
             rc = lib.blkq4_fp16_gemm_sm80(

@@ -98,7 +98,8 @@ extern "C" int blkq4_fp16_gemm_sm100(int block_size, bool column_wise_blocking, 
                                      void const* weights_ptr, size_t weights_size,
                                      void const* scales_ptr, size_t scales_size,
                                      void const* offsets_ptr, size_t offsets_size, void* output_ptr,
-                                     size_t output_size, unsigned flags, void* err) {
+                                     size_t output_size, void const* bias_ptr, size_t bias_size,
+                                     unsigned flags, void* err) {
   if (!blkq4::supported_block(block_size))
     return fail(err, "Unsupported block size: " + std::to_string(block_size));
   if (m <= 0 || n <= 0 || k <= 0)
@@ -131,6 +132,12 @@ extern "C" int blkq4_fp16_gemm_sm100(int block_size, bool column_wise_blocking, 
   if (has_offsets && offsets_size != meta)
     return fail(err, "Unexpected offsets tensor size: " + std::to_string(offsets_size) +
                          " expected: " + std::to_string(meta));
+  const bool has_bias = bias_ptr && bias_size > 0;
+  if (has_bias && bias_size != (size_t)n * sizeof(__half))
+    return fail(err, "Unexpected bias tensor size: " + std::to_string(bias_size) +
+                         " expected: " + std::to_string((size_t)n * sizeof(__half)));
+  if (has_bias && reinterpret_cast<uintptr_t>(bias_ptr) % 4 != 0)
+    return fail(err, "Bias tensor must be 4-byte aligned");
   if (!act_ptr || !weights_ptr || !scales_ptr || !output_ptr)
     return fail(err, "Null tensor pointer");
   if (reinterpret_cast<uintptr_t>(act_ptr) % 16 != 0 ||
@@ -145,13 +152,14 @@ extern "C" int blkq4_fp16_gemm_sm100(int block_size, bool column_wise_blocking, 
   auto s = reinterpret_cast<const __half*>(scales_ptr);
   auto z = has_offsets ? reinterpret_cast<const uint8_t*>(offsets_ptr) : nullptr;
   auto o = reinterpret_cast<__half*>(output_ptr);
+  auto bias = has_bias ? reinterpret_cast<const __half*>(bias_ptr) : nullptr;
 
   // m > 16 is the reference's own threshold between its two tile configurations
   // (src/blkq4_f16_gemm_sm80.cu:343); here it separates the HBM-bound skinny
   // kernel from the tcgen05 tensor-core kernel.
   const std::string e =
-      (m <= 16) ? blkq4::launch_gemv(block_size, column_wise_blocking, m, n, k, stream, a, w, s, z, o, flags)
-                : blkq4::launch_gemm_tc(block_size, column_wise_blocking, m, n, k, stream, a, w, s, z, o);
+      (m <= 16) ? blkq4::launch_gemv(block_size, column_wise_blocking, m, n, k, stream, a, w, s, z, o, bias, flags)
+                : blkq4::launch_gemm_tc(block_size, column_wise_blocking, m, n, k, stream, a, w, s, z, o, bias);
   if (!e.empty()) return fail(err, "Kernel execution failed: " + e);
   return 0;
 }
@@ -164,7 +172,7 @@ extern "C" int blkq4_fp16_gemm_sm80(int block_size, bool column_wise_blocking, i
                                     size_t output_size, void* err) {
   return blkq4_fp16_gemm_sm100(block_size, column_wise_blocking, m, n, k, stream_ptr, act_ptr, a_size,
                                weights_ptr, weights_size, scales_ptr, scales_size, offsets_ptr,
-                               offsets_size, output_ptr, output_size, 0u, err);
+                               offsets_size, output_ptr, output_size, nullptr, 0, 0u, err);
 }
 
 extern "C" void* blkq4_errmsg_create(void) { return new std::string(); }

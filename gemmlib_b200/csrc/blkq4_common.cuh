@@ -27,11 +27,11 @@ std::string launch_quant_prepack(int block, bool colwise, int K, int N, int ld,
 
 std::string launch_gemv(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
                         const __half* a, const uint8_t* packed, const __half* scales,
-                        const uint8_t* zp, __half* out, unsigned flags);
+                        const uint8_t* zp, __half* out, const __half* bias, unsigned flags);
 
 std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
                            const __half* a, const uint8_t* packed, const __half* scales,
-                           const uint8_t* zp, __half* out);
+                           const uint8_t* zp, __half* out, const __half* bias);
 
 // Synchronises `stream` and returns the tensor-core kernel's device error word
 // (0 = every bounded wait completed; -1 = the stream itself reported an error).

@@ -80,6 +80,7 @@ struct Params {
   uint32_t tmem_cols;  // allocation: power of two >= acc_bufs*BM + kDeqStages*kDeqCols
   uint32_t meta_row_bytes_s, meta_row_bytes_z;  // bytes per box row
   __half* out;
+  const __half* bias;  // fp16 [N] added to the fp16 result, or null
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
@@ -375,13 +376,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         tmem_ld_wait();
         int m = m0 + c0 + odd;
         __half* dst = p.out + (size_t)m * p.N + (n & ~1);
+        // The bias is added to the ROUNDED result in fp16, which is what a separate
+        // `output += bias` on the fp16 tensor computes.
+        const bool add_bias = p.bias != nullptr && n_ok;
+        const __half2 bias2 = add_bias ? *reinterpret_cast<const __half2*>(p.bias + (n & ~1)) : __half2();
         const size_t row_step = 2 * (size_t)p.N;
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
           const float mine = __uint_as_float(odd ? r[j + 1] : r[j]);       // my n, my row
           const float give = __uint_as_float(odd ? r[j] : r[j + 1]);       // my n, partner's row
           const float got = __shfl_xor_sync(0xffffffffu, give, 1);          // partner's n, my row
-          const __half2 v = odd ? __floats2half2_rn(got, mine) : __floats2half2_rn(mine, got);
+          __half2 v = odd ? __floats2half2_rn(got, mine) : __floats2half2_rn(mine, got);
+          if (add_bias) v = __hadd2(v, bias2);
           if (n_ok && m < p.M) *reinterpret_cast<__half2*>(dst) = v;
           dst += row_step;
           m += 2;
@@ -504,7 +510,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
 
 std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
                            const __half* a, const uint8_t* packed, const __half* scales,
-                           const uint8_t* zp, __half* out) {
+                           const uint8_t* zp, __half* out, const __half* bias) {
   Params p{};
   p.M = M; p.N = N; p.K = K; p.block = block;
   p.block_shift = block == 16 ? 4 : block == 32 ? 5 : block == 64 ? 6 : 7;
@@ -513,6 +519,7 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
   p.n_tiles = (N + TILE_N - 1) / TILE_N;
   p.has_zp = zp != nullptr;
   p.out = out;
+  p.bias = bias;
   // tensor memory: accumulators first, then the dequantized stages
   p.acc_bufs = (2 * p.BM + kDeqStages * kDeqCols <= 512) ? 2 : 1;
   p.a_col0 = p.acc_bufs * p.BM;

@@ -125,7 +125,7 @@ template <int NT, int MT, int U, bool COLWISE>
 __global__ void __launch_bounds__(kMaxWarps * 32)
 gemv_kernel(const __half* __restrict__ a, const uint8_t* __restrict__ packed,
             const __half* __restrict__ scales, const uint8_t* __restrict__ zps,
-            __half* __restrict__ out, int M, int N, int K, int block) {
+            __half* __restrict__ out, const __half* __restrict__ bias, int M, int N, int K, int block) {
   extern __shared__ float s_red[];  // [warps][NT*MT*4][32]
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -256,7 +256,11 @@ gemv_kernel(const __half* __restrict__ a, const uint8_t* __restrict__ packed,
     const int tile = tile0 + i;
     const int n = tile * 16 + (l >> 2) + 8 * (e >> 1);
     const int m = 8 * j + 2 * (l & 3) + (e & 1);
-    if (tile < ntiles && m < M) out[(size_t)m * N + n] = __float2half_rn(sum);
+    if (tile < ntiles && m < M) {
+      // bias joins the ROUNDED result in fp16, as a separate `output += bias` would
+      const __half h = __float2half_rn(sum);
+      out[(size_t)m * N + n] = bias ? __hadd(h, bias[n]) : h;
+    }
   }
 }
 
@@ -309,6 +313,7 @@ constexpr long long kGemvWaitCycles = 2000000000ll;
 struct PersistParams {
   const __half* a;
   __half* out;
+  const __half* bias;  // fp16 [N] added to the fp16 result, or null
   int M, N, K;
   int block_shift;   // 6 or 7
   int tiles;         // N / 16
@@ -504,7 +509,10 @@ gemv_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
             // accumulator element e of a lane: row n = g + 8 (e >> 1), column m = 8 j + 2 t + (e & 1)
             const int n = tile * 16 + g + 8 * (e >> 1);
             const int m = 8 * j + 2 * t + (e & 1);
-            if (m < p.M) p.out[(size_t)m * p.N + n] = __float2half_rn(sum);
+            if (m < p.M) {
+              const __half h = __float2half_rn(sum);
+              p.out[(size_t)m * p.N + n] = p.bias ? __hadd(h, p.bias[n]) : h;
+            }
           }
         __syncwarp();
         if (lane == 0) {
@@ -609,9 +617,9 @@ static int env_int(const char* name) {
 template <int MT, bool HAS_ZP>
 std::string launch_persistent_T(int M, int N, int K, int block, cudaStream_t stream, const __half* a,
                                 const uint8_t* packed, const __half* scales, const uint8_t* zp,
-                                __half* out, bool early_fetch) {
+                                __half* out, const __half* bias, bool early_fetch) {
   PersistParams p{};
-  p.a = a; p.out = out; p.M = M; p.N = N; p.K = K;
+  p.a = a; p.out = out; p.bias = bias; p.M = M; p.N = N; p.K = K;
   p.block_shift = block == 64 ? 6 : 7;
   p.tiles = N / 16;
   p.nsub = K / kUnitKBytes;
@@ -663,7 +671,7 @@ std::string launch_persistent_T(int M, int N, int K, int block, cudaStream_t str
 template <int NT, int MT, int U, bool COLWISE>
 cudaError_t launch_T(int warps, int M, int N, int K, int block, cudaStream_t stream,
                      const __half* a, const uint8_t* packed, const __half* scales,
-                     const uint8_t* zp, __half* out) {
+                     const uint8_t* zp, __half* out, const __half* bias) {
   const int ntiles = N / 16;
   const int grid = (ntiles + NT - 1) / NT;
   const size_t smem = (size_t)warps * NT * MT * 4 * 32 * sizeof(float);
@@ -672,7 +680,7 @@ cudaError_t launch_T(int warps, int M, int N, int K, int block, cudaStream_t str
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
-  kern<<<grid, warps * 32, smem, stream>>>(a, packed, scales, zp, out, M, N, K, block);
+  kern<<<grid, warps * 32, smem, stream>>>(a, packed, scales, zp, out, bias, M, N, K, block);
   return cudaGetLastError();
 }
 
@@ -686,7 +694,7 @@ int read_gemv_error() {
 
 std::string launch_gemv(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
                         const __half* a, const uint8_t* packed, const __half* scales,
-                        const uint8_t* zp, __half* out, unsigned flags) {
+                        const uint8_t* zp, __half* out, const __half* bias, unsigned flags) {
   if (M < 1 || M > 16) return "skinny kernel needs 1 <= M <= 16";
   const bool early = (flags & BLKQ4_GEMM_EARLY_WEIGHT_FETCH) != 0;
   static const int env_warps = env_int("BLKQ4_GEMV_WARPS"), env_u = env_int("BLKQ4_GEMV_U");
@@ -703,23 +711,23 @@ std::string launch_gemv(int block, bool colwise, int M, int N, int K, cudaStream
   if (colwise && block >= 64 && !env_generic && K % kUnitKBytes == 0 && K <= 32768 &&
       reinterpret_cast<uintptr_t>(scales) % 16 == 0 && (!zp || reinterpret_cast<uintptr_t>(zp) % 16 == 0)) {
     if (M <= 8)
-      return zp ? launch_persistent_T<1, true>(M, N, K, block, stream, a, packed, scales, zp, out, early)
-                : launch_persistent_T<1, false>(M, N, K, block, stream, a, packed, scales, zp, out, early);
-    return zp ? launch_persistent_T<2, true>(M, N, K, block, stream, a, packed, scales, zp, out, early)
-              : launch_persistent_T<2, false>(M, N, K, block, stream, a, packed, scales, zp, out, early);
+      return zp ? launch_persistent_T<1, true>(M, N, K, block, stream, a, packed, scales, zp, out, bias, early)
+                : launch_persistent_T<1, false>(M, N, K, block, stream, a, packed, scales, zp, out, bias, early);
+    return zp ? launch_persistent_T<2, true>(M, N, K, block, stream, a, packed, scales, zp, out, bias, early)
+              : launch_persistent_T<2, false>(M, N, K, block, stream, a, packed, scales, zp, out, bias, early);
   }
   // Row-wise blocking carries 48 bytes of meta per chunk in registers, so it fetches
   // fewer steps at a time.
   if (M <= 8) {
     if (colwise)
-      e = (u >= 8) ? launch_T<1, 1, 8, true>(warps, M, N, K, block, stream, a, packed, scales, zp, out)
-          : (u <= 2) ? launch_T<1, 1, 2, true>(warps, M, N, K, block, stream, a, packed, scales, zp, out)
-                     : launch_T<1, 1, 4, true>(warps, M, N, K, block, stream, a, packed, scales, zp, out);
+      e = (u >= 8) ? launch_T<1, 1, 8, true>(warps, M, N, K, block, stream, a, packed, scales, zp, out, bias)
+          : (u <= 2) ? launch_T<1, 1, 2, true>(warps, M, N, K, block, stream, a, packed, scales, zp, out, bias)
+                     : launch_T<1, 1, 4, true>(warps, M, N, K, block, stream, a, packed, scales, zp, out, bias);
     else
-      e = launch_T<1, 1, 2, false>(warps, M, N, K, block, stream, a, packed, scales, zp, out);
+      e = launch_T<1, 1, 2, false>(warps, M, N, K, block, stream, a, packed, scales, zp, out, bias);
   } else {
-    e = colwise ? launch_T<2, 2, 2, true>(warps, M, N, K, block, stream, a, packed, scales, zp, out)
-                : launch_T<2, 2, 1, false>(warps, M, N, K, block, stream, a, packed, scales, zp, out);
+    e = colwise ? launch_T<2, 2, 2, true>(warps, M, N, K, block, stream, a, packed, scales, zp, out, bias)
+                : launch_T<2, 2, 1, false>(warps, M, N, K, block, stream, a, packed, scales, zp, out, bias);
   }
   if (e != cudaSuccess) return std::string(cudaGetErrorString(e));
   return std::string();

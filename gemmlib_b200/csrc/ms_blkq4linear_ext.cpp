@@ -8,7 +8,9 @@
 //   - with has_offsets == false `quant` returns an empty uint8 tensor for the zero
 //     points (the reference returns an undefined tensor, which its own `forward`
 //     cannot accept);
-//   - `forward_out` writes into a caller-provided output tensor.
+//   - `forward_out` writes into a caller-provided output tensor and takes an optional fp16 bias
+//     (added in the kernel epilogue, bit-identical to `output += bias`) and the flags of
+//     blkq4_fp16_gemm_sm100.
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 #include <torch/extension.h>
@@ -58,7 +60,8 @@ std::vector<torch::Tensor> blkq4linear_quant(int block_size, bool col_wise, bool
 
 torch::Tensor blkq4linear_forward_out(int block_size, bool col_wise, int in_features, int out_features,
                                       torch::Tensor input, torch::Tensor q_weights, torch::Tensor q_scales,
-                                      torch::Tensor q_zp, torch::Tensor output) {
+                                      torch::Tensor q_zp, torch::Tensor output,
+                                      c10::optional<torch::Tensor> bias, int64_t flags) {
   TORCH_CHECK(input.scalar_type() == torch::kFloat16, "blkq4linear_forward only supports float16 inputs");
   TORCH_CHECK(input.dim() == 2 && input.size(1) == in_features,
               "Activation shape is not compatible with the weights");
@@ -72,16 +75,23 @@ torch::Tensor blkq4linear_forward_out(int block_size, bool col_wise, int in_feat
                   output.size(0) == input.size(0) && output.size(1) == out_features,
               "Output tensor must be a contiguous float16 [batch, out_features] tensor");
 
+  const bool has_bias = bias.has_value() && bias->defined() && bias->numel() > 0;
+  if (has_bias)
+    TORCH_CHECK(bias->scalar_type() == torch::kFloat16 && bias->is_contiguous() && bias->device() == dev &&
+                    bias->numel() == out_features,
+                "Fused bias must be a contiguous float16 [out_features] tensor on the input's device");
+
   const c10::cuda::CUDAGuard guard(dev);
   const bool has_zp = q_zp.defined() && q_zp.numel() > 0;
   std::string err;
-  int rc = blkq4_fp16_gemm_sm80(block_size, col_wise, int(input.size(0)), out_features, in_features,
-                                c10::cuda::getCurrentCUDAStream().stream(), input.data_ptr(),
-                                size_t(input.numel()) * kHalfBytes, q_weights.data_ptr(),
+  int rc = blkq4_fp16_gemm_sm100(block_size, col_wise, int(input.size(0)), out_features, in_features,
+                                 c10::cuda::getCurrentCUDAStream().stream(), input.data_ptr(),
+                                 size_t(input.numel()) * kHalfBytes, q_weights.data_ptr(),
                                 size_t(q_weights.numel()), q_scales.data_ptr(),
                                 size_t(q_scales.numel()) * kHalfBytes, has_zp ? q_zp.data_ptr() : nullptr,
                                 has_zp ? size_t(q_zp.numel()) : 0, output.data_ptr(),
-                                size_t(output.numel()) * kHalfBytes, &err);
+                                size_t(output.numel()) * kHalfBytes, has_bias ? bias->data_ptr() : nullptr,
+                                has_bias ? size_t(bias->numel()) * kHalfBytes : 0, unsigned(flags), &err);
   TORCH_CHECK(rc == 0, err);
   return output;
 }
@@ -93,7 +103,7 @@ torch::Tensor blkq4linear_forward(int block_size, bool col_wise, int in_features
   auto output = torch::empty({input.size(0), out_features},
                              torch::TensorOptions().dtype(torch::kFloat16).device(input.device()));
   return blkq4linear_forward_out(block_size, col_wise, in_features, out_features, input, q_weights, q_scales,
-                                 q_zp, output);
+                                 q_zp, output, c10::nullopt, 0);
 }
 
 }  // namespace
@@ -101,6 +111,10 @@ torch::Tensor blkq4linear_forward(int block_size, bool col_wise, int in_features
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("quant", &blkq4linear_quant, "Quantize float 16 weights");
   m.def("forward", &blkq4linear_forward, "Forward pass for block quantized linear layer");
-  m.def("forward_out", &blkq4linear_forward_out, "Forward pass into a caller-provided output tensor");
+  m.def("forward_out", &blkq4linear_forward_out, "Forward pass into a caller-provided output tensor",
+        py::arg("block_size"), py::arg("col_wise"), py::arg("in_features"), py::arg("out_features"),
+        py::arg("input"), py::arg("q_weights"), py::arg("q_scales"), py::arg("q_zp"), py::arg("output"),
+        py::arg("bias") = py::none(), py::arg("flags") = 0);
+  m.attr("EARLY_WEIGHT_FETCH") = int(BLKQ4_GEMM_EARLY_WEIGHT_FETCH);
   m.def("library_version", []() { return std::string(blkq4_version()); });
 }

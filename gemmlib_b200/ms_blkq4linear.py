@@ -9,7 +9,12 @@ W4A16 GEMM/GEMV and adds the bias.
 Additive differences: the packed tensors are registered as buffers, so they travel
 with ``state_dict()`` / ``.to()``; the constructor's diagnostic prints are gone;
 ``from_packed`` rebuilds a layer from already-quantized tensors; inputs with leading
-batch dimensions are flattened to 2-D and restored.
+batch dimensions are flattened to 2-D and restored; ``forward(input, out=...)`` writes
+into a caller's tensor; a float16 bias on the layer's device is added inside the kernel's
+epilogue (bit-identical to the reference's separate ``output += bias``, one pass over the
+output less); and, from the second call on, the skinny kernel is launched with
+``BLKQ4_GEMM_EARLY_WEIGHT_FETCH`` (set ``early_weight_fetch = False`` on a layer whose
+packed tensors are rewritten by work queued on the same stream as ``forward``).
 """
 from __future__ import annotations
 
@@ -34,6 +39,8 @@ class BlkQ4Linear(nn.Module):
         self.register_buffer("q_scales", q_scales)
         self.register_buffer("q_zp", q_zp)
         self.bias = bias_tensor
+        self.early_weight_fetch = True
+        self._settled = False  # the first forward is a plain launch, ordered after the quantizer
 
     @classmethod
     def from_packed(cls, block_size, col_wise, in_features, out_features, q_weights, q_scales, q_zp=None,
@@ -50,20 +57,35 @@ class BlkQ4Linear(nn.Module):
         self.register_buffer("q_scales", q_scales)
         self.register_buffer("q_zp", q_zp)
         self.bias = bias_tensor
+        self.early_weight_fetch = True
+        self._settled = False
         return self
+
+    def _load_from_state_dict(self, *args, **kwargs):
+        self._settled = False  # the buffers are about to be overwritten by a copy on some stream
+        return super()._load_from_state_dict(*args, **kwargs)
+
+    def _fusable_bias(self, x):
+        b = self.bias
+        if (b is not None and b.dtype == torch.float16 and b.device == x.device and b.dim() == 1
+                and b.numel() == self.out_features and b.is_contiguous()):
+            return b
+        return None
 
     def forward(self, input, out=None):
         lead = input.shape[:-1]
         x = input.reshape(-1, self.in_features)
         if out is None:
-            output = ms_blkq4linear_ext.forward(
-                self.block_size, self.col_wise, self.in_features, self.out_features,
-                x, self.q_weights, self.q_scales, self.q_zp)
+            output = torch.empty(x.size(0), self.out_features, dtype=torch.float16, device=x.device)
         else:
-            output = ms_blkq4linear_ext.forward_out(
-                self.block_size, self.col_wise, self.in_features, self.out_features,
-                x, self.q_weights, self.q_scales, self.q_zp, out.view(-1, self.out_features))
-        if self.bias is not None:
+            output = out.view(-1, self.out_features)
+        fused = self._fusable_bias(x)
+        flags = ms_blkq4linear_ext.EARLY_WEIGHT_FETCH if (self.early_weight_fetch and self._settled) else 0
+        ms_blkq4linear_ext.forward_out(
+            self.block_size, self.col_wise, self.in_features, self.out_features,
+            x, self.q_weights, self.q_scales, self.q_zp, output, fused, flags)
+        self._settled = True
+        if self.bias is not None and fused is None:
             output += self.bias
         return output.view(*lead, self.out_features)
 

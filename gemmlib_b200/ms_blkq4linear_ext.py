@@ -4,7 +4,7 @@
 Exposes the reference extension's functions (python/ms_blkq4linear_ext/
 ms_blkq4linear.cpp:120-123): ``quant(block_size, col_wise, has_offsets, weights)``
 and ``forward(block_size, col_wise, in_features, out_features, input, q_weights,
-q_scales, q_zp)``, plus ``forward_out``.  There is no Python or CPU fallback: a
+q_scales, q_zp)``, plus ``forward_out(..., output, bias=None, flags=0)``.  There is no Python or CPU fallback: a
 missing binary is an ImportError.
 """
 import importlib.util
@@ -29,3 +29,4 @@ quant = _mod.quant
 forward = _mod.forward
 forward_out = _mod.forward_out
 library_version = _mod.library_version
+EARLY_WEIGHT_FETCH = _mod.EARLY_WEIGHT_FETCH

@@ -106,8 +106,14 @@ int blkq4_fp16_quant_size_sm80(
     void* error_message);
 
 /**
- * blkq4_fp16_gemm_sm80 with a `flags` word; flags = 0 is exactly that call.  No counterpart in
- * the reference (its signature is reference include/ms_blkq4gemm.h:41-50 plus `flags`).
+ * blkq4_fp16_gemm_sm80 with an optional bias and a `flags` word; without bias and with flags = 0
+ * it is exactly that call.  No counterpart in the reference (the signature is reference
+ * include/ms_blkq4gemm.h:41-50 plus the three arguments; the bias replaces the separate
+ * `output += bias` of the reference module, python/ms_blkq4linear.py:26-27).
+ *
+ * bias_ptr: fp16 [N] (bias_size = 2*N bytes, 4-byte aligned), or null / size 0.  It is added in
+ * fp16 to the result already rounded to fp16, so the output is bit-identical to running the GEMM
+ * and then adding the bias to the fp16 output tensor, without the extra pass over [M, N].
  *
  * BLKQ4_GEMM_EARLY_WEIGHT_FETCH: the caller vouches that weights, scales and offsets are not
  * written by any work still pending on `stream` (inference weights, quantized once).  The
@@ -127,6 +133,7 @@ int blkq4_fp16_gemm_sm100(
   void const* scales_ptr, size_t scales_size,
   void const* offsets_ptr, size_t offsets_size,
   void* output_ptr, size_t output_size,
+  void const* bias_ptr, size_t bias_size,
   unsigned flags,
   void* error_message);
 

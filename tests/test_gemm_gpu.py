@@ -140,6 +140,30 @@ def test_early_weight_fetch_keeps_stream_order_for_activations():
         assert np.abs(x - y).max() <= 2.0 ** -8 * max(1.0, np.abs(x).max()), i
 
 
+@pytest.mark.parametrize("case", [(64, True, False, 1, 2048, 1024), (64, True, True, 12, 352, 256),
+                                  (32, False, True, 5, 96, 192), (32, True, True, 300, 384, 512),
+                                  (128, True, False, 64, 256, 384)], ids=lambda c: "-".join(map(str, c)))
+def test_fused_bias_equals_separate_add(case):
+    """The bias of blkq4_fp16_gemm_sm100 is added in fp16 to the rounded result: bit-identical
+    to the reference module's `output += bias` on the fp16 output (every kernel family)."""
+    from gemmlib_b200 import capi
+
+    block, colwise, has_zp, M, N, K = case
+    w = gaussian_weight(N, K, seed=7)
+    a = to_cuda(gaussian_act(M, K, seed=8).numpy())
+    pw, ps, pz = (to_cuda(x) for x in O.quant_prepack(block, colwise, w.numpy(), has_zp))
+    bias = (torch.randn(N, generator=torch.Generator().manual_seed(9)) * 0.5).to(torch.float16).cuda()
+    plain = torch.empty(M, N, dtype=torch.float16, device="cuda")
+    fused = torch.empty_like(plain)
+    capi.gemm(block, colwise, M, N, K, a, pw, ps, pz, plain)
+    capi.gemm(block, colwise, M, N, K, a, pw, ps, pz, fused, bias=bias)
+    torch.cuda.synchronize()
+    plain += bias
+    assert torch.equal(plain.view(torch.int16), fused.view(torch.int16))
+    with pytest.raises(capi.BlkQ4Error, match="bias"):
+        capi.gemm(block, colwise, M, N, K, a, pw, ps, pz, fused, bias=bias[:-2])
+
+
 def test_config_c1_cpu_reference_case():
     """configs[0]: M16 K4096 N4096 b32 column-wise with zero points."""
     check_gaussian(32, True, True, 16, 4096, 4096)
