@@ -347,6 +347,10 @@ def run_ours(args):
     if world == 1:
         line["quant_prepack"] = bench_quant(torch, dev, peaks)
         line["gemm"] = bench_gemm_c3(torch, dev, peaks)
+        try:
+            line["reference_gpu"] = bench_reference_gpu(torch, dev, layers, a_dev)
+        except Exception as exc:  # a baseline must never cost the measurement
+            line["reference_gpu"] = {"unavailable": "%s: %s" % (type(exc).__name__, exc)}
         gbs, sec, passes, threads = cpu_dequant_gemm_sample(cfg)
         line["cpu_baseline"] = {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port",
                                 "sample": f"one c2 layer, {passes} passes of oracle dequantize+GEMV, median {sec * 1e3:.1f} ms per pass"}
@@ -401,6 +405,98 @@ def bench_quant(torch, dev, peaks):
             "value": round(gbs, 1), "unit": "GB/s", "us_per_call": round(us, 2),
             "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": round(gbs / peaks["hbm_gbs"], 4), "peak_source": peaks["source"]}}
+
+
+def bench_reference_gpu(torch, dev, layers_c2, a_dev):
+    """The reference's own CUDA kernels (its sm80-class mma.sync path, compiled for sm_100a from
+    its sources into oracle/_ref by `make -C oracle ref_gpu`) on the same B200, same packed
+    tensors: the decode GEMV over the bench's 16 layers and the prefill GEMM.  A reported
+    baseline next to this library's numbers; nothing of it is on the measured path."""
+    import ctypes
+
+    path = os.path.join(ROOT, "oracle", "_ref", "libms_blkq4gemm_ref.so")
+    if not os.path.exists(path):
+        return {"unavailable": "oracle/_ref/libms_blkq4gemm_ref.so not built (make -C oracle ref_gpu)"}
+    ref = ctypes.CDLL(path)
+    vp, sz = ctypes.c_void_p, ctypes.c_size_t
+    ref.blkq4_fp16_gemm_sm80.argtypes = [ctypes.c_int, ctypes.c_bool] + [ctypes.c_int] * 3 + [vp] + [vp, sz] * 5 + [vp]
+    ref.blkq4_fp16_gemm_sm80.restype = ctypes.c_int
+
+    def call(block, cw, M, N, K, stream, a, qw, qs, qz, o):
+        zp = qz if (qz is not None and qz.numel()) else None
+        rc = ref.blkq4_fp16_gemm_sm80(
+            block, cw, M, N, K, stream, a.data_ptr(), a.numel() * 2, qw.data_ptr(), qw.numel(),
+            qs.data_ptr(), qs.numel() * 2, zp.data_ptr() if zp is not None else None,
+            zp.numel() if zp is not None else 0, o.data_ptr(), o.numel() * 2, None)
+        if rc != 0:
+            raise RuntimeError("reference GEMM returned %d" % rc)
+
+    out = {}
+    stream = torch.cuda.Stream()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # ---- decode GEMV, the bench's own layers ----
+    c = C2
+    o_ref = torch.empty(c["M"], c["N"], dtype=torch.float16, device=dev)
+    o_our = torch.empty_like(o_ref)
+
+    def step_ref(st):
+        for lyr in layers_c2:
+            call(c["block"], True, c["M"], c["N"], c["K"], st, a_dev, lyr.q_weights, lyr.q_scales, lyr.q_zp, o_ref)
+
+    with torch.cuda.stream(stream):
+        step_ref(stream.cuda_stream)
+    torch.cuda.synchronize()
+    layers_c2[-1](a_dev, out=o_our)
+    torch.cuda.synchronize()
+    out["c2_max_abs_diff_vs_ours"] = float((o_ref.float() - o_our.float()).abs().max())
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step_ref(stream.cuda_stream)
+        run, how = graph.replay, "CUDA-graph replay"
+    except Exception:  # the reference's launcher is not capturable: time plain launches
+        torch.cuda.synchronize()
+        run, how = (lambda: step_ref(0)), "plain launches"
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    reps = 100
+    e0.record()
+    for _ in range(reps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (reps * len(layers_c2))
+    nbytes = algorithmic_bytes(c["M"], c["K"], c["N"], c["block"], True, False)
+    out["c2_gemv"] = {"us_per_launch": round(us, 2), "GB/s": round(nbytes / us / 1e3, 1), "timing": how}
+    # ---- prefill GEMM ----
+    from gemmlib_b200.ms_blkq4linear import BlkQ4Linear
+    c = C3
+    sets = 4
+    g = torch.Generator().manual_seed(100)
+    lyrs = [BlkQ4Linear(c["block"], True, False, (torch.randn(c["N"], c["K"], generator=g) * c["sigma"]).half().to(dev))
+            for _ in range(sets)]
+    acts = [torch.randn(c["M"], c["K"], generator=g).half().to(dev) for _ in range(sets)]
+    outs = [torch.empty(c["M"], c["N"], dtype=torch.float16, device=dev) for _ in range(sets)]
+    for _ in range(2):
+        for lyr, x, o in zip(lyrs, acts, outs):
+            call(c["block"], True, c["M"], c["N"], c["K"], 0, x, lyr.q_weights, lyr.q_scales, lyr.q_zp, o)
+    torch.cuda.synchronize()
+    ours = lyrs[0](acts[0])
+    torch.cuda.synchronize()
+    out["c3_max_abs_diff_vs_ours"] = float((outs[0].float() - ours.float()).abs().max())
+    reps = 10
+    e0.record()
+    for _ in range(reps):
+        for lyr, x, o in zip(lyrs, acts, outs):
+            call(c["block"], True, c["M"], c["N"], c["K"], 0, x, lyr.q_weights, lyr.q_scales, lyr.q_zp, o)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (reps * sets)
+    out["c3_gemm"] = {"us_per_call": round(us, 2), "TFLOP/s": round(2.0 * c["M"] * c["N"] * c["K"] / us / 1e6, 1),
+                      "timing": "plain launches"}
+    out["what"] = "reference CUDA kernels (mma.sync path) compiled for sm_100a, same packed tensors, same GPU"
+    return out
 
 
 def bench_gemm_c3(torch, dev, peaks):
