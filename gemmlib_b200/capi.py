@@ -23,6 +23,11 @@ SYMBOLS = (
     "blkq4_errmsg_cstr",
     "blkq4_errmsg_destroy",
     "blkq4_last_kernel_status",
+    "blkq4_gather_create",
+    "blkq4_gather_connect",
+    "blkq4_fp16_gemm_gather_sm100",
+    "blkq4_gather_status",
+    "blkq4_gather_destroy",
     "blkq4_version",
 )
 
@@ -55,6 +60,17 @@ def _load() -> ctypes.CDLL:
     lib.blkq4_version.restype = ctypes.c_char_p
     lib.blkq4_last_kernel_status.argtypes = [vp]
     lib.blkq4_last_kernel_status.restype = i
+    lib.blkq4_gather_create.argtypes = [i, i, sz, ctypes.POINTER(vp), vp, vp]
+    lib.blkq4_gather_create.restype = i
+    lib.blkq4_gather_connect.argtypes = [vp, vp, vp]
+    lib.blkq4_gather_connect.restype = i
+    lib.blkq4_fp16_gemm_gather_sm100.argtypes = [vp, i, b, i, i, i, vp, vp, sz, vp, sz, vp, sz, vp, sz, vp, sz,
+                                                 ctypes.c_uint, vp]
+    lib.blkq4_fp16_gemm_gather_sm100.restype = i
+    lib.blkq4_gather_status.argtypes = [vp, vp]
+    lib.blkq4_gather_status.restype = i
+    lib.blkq4_gather_destroy.argtypes = [vp]
+    lib.blkq4_gather_destroy.restype = i
     return lib
 
 
@@ -140,3 +156,56 @@ def gemm(block_size, column_wise, m, n, k, act, q_weights, q_scales, q_zp, out, 
             )
         if rc != 0:
             raise BlkQ4Error(e.text())
+
+
+class GatherContext:
+    """One rank's side of the fused GEMM + all-gather (``blkq4_gather_*``).
+
+    ``handle`` (64 bytes) is this rank's IPC handle; collect the handles of all ranks, ordered
+    by rank, and pass them to :meth:`connect` before the first :meth:`gemm`.
+    """
+
+    def __init__(self, world: int, rank: int, max_out_bytes: int):
+        self.world, self.rank = int(world), int(rank)
+        self._ctx = ctypes.c_void_p()
+        buf = ctypes.create_string_buffer(64)
+        with _ErrMsg() as e:
+            if lib.blkq4_gather_create(world, rank, max_out_bytes, ctypes.byref(self._ctx), buf, e.p) != 0:
+                raise BlkQ4Error(e.text())
+        self.handle = bytes(buf.raw)
+
+    def connect(self, handles):
+        blob = b"".join(handles)
+        if len(blob) != 64 * self.world:
+            raise ValueError("need one 64-byte handle per rank")
+        with _ErrMsg() as e:
+            if lib.blkq4_gather_connect(self._ctx, blob, e.p) != 0:
+                raise BlkQ4Error(e.text())
+
+    def gemm(self, block_size, column_wise, m, n_shard, k, act, q_weights, q_scales, q_zp, out_full, stream=0,
+             flags=0):
+        ap, as_ = _ptr_size(act)
+        qp, qs = _ptr_size(q_weights)
+        sp, ss = _ptr_size(q_scales)
+        zp, zs = _ptr_size(q_zp)
+        op, os_ = _ptr_size(out_full)
+        with _ErrMsg() as e:
+            rc = lib.blkq4_fp16_gemm_gather_sm100(
+                self._ctx, block_size, column_wise, m, n_shard, k, stream, ap, as_, qp, qs, sp, ss, zp, zs,
+                op, os_, flags, e.p)
+            if rc != 0:
+                raise BlkQ4Error(e.text())
+
+    def status(self, stream=0) -> int:
+        return int(lib.blkq4_gather_status(self._ctx, stream))
+
+    def close(self):
+        if self._ctx:
+            lib.blkq4_gather_destroy(self._ctx)
+            self._ctx = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -29,6 +29,30 @@ std::string launch_gemv(int block, bool colwise, int M, int N, int K, cudaStream
                         const __half* a, const uint8_t* packed, const __half* scales,
                         const uint8_t* zp, __half* out, const __half* bias, unsigned flags);
 
+// ---- fused GEMV + all-gather over peer memory (one process per GPU, one box) ----------------
+// Every rank owns one device block, mapped by all peers (CUDA IPC):
+//   [0]   uint32 epoch      layer calls completed by this rank
+//   [4]   uint32 done_ctr   CTAs of the running call that have finished storing
+//   [8]   int    error      first wait that expired (0 = none)
+//   [64]  uint32 flags[2][kGatherMaxRanks]   flags[slot][src] = epoch whose slice from `src` landed
+//   [kGatherCtrlBytes]  gathered[2][buf_bytes]  the [M, N_total] results of even / odd epochs
+constexpr int kGatherMaxRanks = 8;
+constexpr int kGatherCtrlBytes = 1024;
+constexpr int kGatherEpochOff = 0, kGatherDoneOff = 4, kGatherErrorOff = 8, kGatherFlagsOff = 64;
+
+struct GatherTable {
+  uint8_t* base[kGatherMaxRanks];  // every rank's block; base[rank] is the local one
+  int world, rank;                 // world == 0: no gather (plain output)
+  int n_total;                     // columns of the gathered output = world * N
+  unsigned long long buf_bytes;    // bytes of one gathered buffer
+};
+
+// The skinny kernel with its epilogue storing this rank's [M, N] slice straight into every
+// rank's gathered buffer.  Returns "unsupported" when the shape is not on the TMA fast path.
+std::string launch_gemv_gather(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
+                               const __half* a, const uint8_t* packed, const __half* scales,
+                               const uint8_t* zp, const GatherTable& gt, unsigned flags);
+
 std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
                            const __half* a, const uint8_t* packed, const __half* scales,
                            const uint8_t* zp, __half* out, const __half* bias);

@@ -314,6 +314,7 @@ struct PersistParams {
   const __half* a;
   __half* out;
   const __half* bias;  // fp16 [N] added to the fp16 result, or null
+  GatherTable gt;      // gt.world > 0: the result goes to every rank's gathered buffer instead of `out`
   int M, N, K;
   int block_shift;   // 6 or 7
   int tiles;         // N / 16
@@ -352,6 +353,7 @@ gemv_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   volatile int* abort_flag = reinterpret_cast<volatile int*>(s_raw + 16 * kRing);
   int* s_cnt = reinterpret_cast<int*>(s_raw + 16 * kRing + 16);        // [kAccBufs] arrivals
   volatile int* s_gen = reinterpret_cast<volatile int*>(s_cnt + kAccBufs);  // [kAccBufs] tiles finalized
+  int* s_done = const_cast<int*>(s_gen) + kAccBufs;                          // consumer warps finished (gather)
   uint8_t* s_ring = s_raw + kCtrlBytes;
   float* s_acc = reinterpret_cast<float*>(s_ring + kRing * kSlotBytes);   // [kAccBufs][VALS][32]
   float* s_corr = s_acc + kAccBufs * VALS * 32;                            // [steps][MR][CW]
@@ -373,6 +375,7 @@ gemv_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
     }
     *abort_flag = 0;
     for (int i = 0; i < kAccBufs; ++i) { s_cnt[i] = 0; s_gen[i] = 0; }
+    *s_done = 0;
     mbar_init_fence();
   }
   for (int i = threadIdx.x; i < kAccBufs * VALS * 32; i += blockDim.x) s_acc[i] = 0.0f;
@@ -468,6 +471,14 @@ gemv_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
 
     float total[MT][4];
     int cur_lt = -1;
+    // Gather mode: the call's epoch is one past the calls completed so far (the word only changes
+    // when every CTA of this call has finished); even / odd epochs alternate between two buffers.
+    unsigned gather_epoch = 0;
+    size_t gather_off = 0;
+    if (p.gt.world > 0) {
+      gather_epoch = *reinterpret_cast<volatile unsigned*>(p.gt.base[p.gt.rank] + kGatherEpochOff) + 1u;
+      gather_off = kGatherCtrlBytes + (size_t)(gather_epoch & 1u) * p.gt.buf_bytes;
+    }
 
     // Adds this warp's partial sums of local tile `lt` to the tile's shared accumulator; the
     // warp that completes the tile rounds to fp16, stores, and recycles the accumulator.
@@ -511,7 +522,13 @@ gemv_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
             const int m = 8 * j + 2 * t + (e & 1);
             if (m < p.M) {
               const __half h = __float2half_rn(sum);
-              p.out[(size_t)m * p.N + n] = p.bias ? __hadd(h, p.bias[n]) : h;
+              if (p.gt.world > 0) {
+                // this rank's columns of the gathered [M, n_total] result, in every rank's buffer
+                const size_t off = gather_off + ((size_t)m * p.gt.n_total + (size_t)p.gt.rank * p.N + n) * sizeof(__half);
+                for (int r = 0; r < p.gt.world; ++r) *reinterpret_cast<__half*>(p.gt.base[r] + off) = h;
+              } else {
+                p.out[(size_t)m * p.N + n] = p.bias ? __hadd(h, p.bias[n]) : h;
+              }
             }
           }
         __syncwarp();
@@ -604,6 +621,27 @@ gemv_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       if (lane == 0) mbar_arrive(bar_empty + 8 * slot);
     }
     if (ok && cur_lt >= 0) flush(cur_lt);
+    if (p.gt.world > 0 && ok) {
+      // Publish: every storing thread fences its peer stores to system scope; the last consumer
+      // warp of the CTA counts the CTA in; the last CTA of the grid advances the local epoch and
+      // raises this rank's flag in every rank's block.
+      __threadfence_system();
+      __syncwarp();
+      if (lane == 0 && atomicAdd(s_done, 1) == kCons - 1) {
+        uint8_t* local = p.gt.base[p.gt.rank];
+        __threadfence();
+        const unsigned arrived = atomicAdd(reinterpret_cast<unsigned*>(local + kGatherDoneOff), 1u);
+        if (arrived == gridDim.x - 1) {
+          __threadfence_system();
+          *reinterpret_cast<volatile unsigned*>(local + kGatherDoneOff) = 0u;
+          *reinterpret_cast<volatile unsigned*>(local + kGatherEpochOff) = gather_epoch;
+          __threadfence_system();
+          const size_t foff = kGatherFlagsOff + ((gather_epoch & 1u) * kGatherMaxRanks + p.gt.rank) * sizeof(unsigned);
+          for (int r = 0; r < p.gt.world; ++r)
+            *reinterpret_cast<volatile unsigned*>(p.gt.base[r] + foff) = gather_epoch;
+        }
+      }
+    }
   }
 }
 
@@ -617,9 +655,11 @@ static int env_int(const char* name) {
 template <int MT, bool HAS_ZP>
 std::string launch_persistent_T(int M, int N, int K, int block, cudaStream_t stream, const __half* a,
                                 const uint8_t* packed, const __half* scales, const uint8_t* zp,
-                                __half* out, const __half* bias, bool early_fetch) {
+                                __half* out, const __half* bias, bool early_fetch,
+                                const GatherTable* gt = nullptr) {
   PersistParams p{};
-  p.a = a; p.out = out; p.bias = bias; p.M = M; p.N = N; p.K = K;
+  p.a = a; p.out = out; p.bias = bias;
+  if (gt) p.gt = *gt; p.M = M; p.N = N; p.K = K;
   p.block_shift = block == 64 ? 6 : 7;
   p.tiles = N / 16;
   p.nsub = K / kUnitKBytes;
@@ -731,6 +771,21 @@ std::string launch_gemv(int block, bool colwise, int M, int N, int K, cudaStream
   }
   if (e != cudaSuccess) return std::string(cudaGetErrorString(e));
   return std::string();
+}
+
+std::string launch_gemv_gather(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
+                               const __half* a, const uint8_t* packed, const __half* scales,
+                               const uint8_t* zp, const GatherTable& gt, unsigned flags) {
+  if (M < 1 || M > 16) return "unsupported: the fused gather needs 1 <= M <= 16";
+  if (!(colwise && block >= 64 && K % kUnitKBytes == 0 && K <= 32768 &&
+        reinterpret_cast<uintptr_t>(scales) % 16 == 0 && (!zp || reinterpret_cast<uintptr_t>(zp) % 16 == 0)))
+    return "unsupported: the fused gather runs on the column-wise block >= 64 fast path only";
+  const bool early = (flags & BLKQ4_GEMM_EARLY_WEIGHT_FETCH) != 0;
+  if (M <= 8)
+    return zp ? launch_persistent_T<1, true>(M, N, K, block, stream, a, packed, scales, zp, nullptr, nullptr, early, &gt)
+              : launch_persistent_T<1, false>(M, N, K, block, stream, a, packed, scales, zp, nullptr, nullptr, early, &gt);
+  return zp ? launch_persistent_T<2, true>(M, N, K, block, stream, a, packed, scales, zp, nullptr, nullptr, early, &gt)
+            : launch_persistent_T<2, false>(M, N, K, block, stream, a, packed, scales, zp, nullptr, nullptr, early, &gt);
 }
 
 }  // namespace blkq4

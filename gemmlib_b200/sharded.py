@@ -3,10 +3,13 @@
 The weight [out_features, in_features] is split along out_features (N); rank r owns
 rows [r*N/g, (r+1)*N/g), quantizes and prepacks its shard locally, and computes
 ``out_r = input @ W_r^T`` for the replicated input.  The only exchange is an
-all-gather of the outputs along the last dimension at the layer boundary
-(``torch.distributed``, NCCL over NVLink on GPUs; gloo in the CPU tests of the
-partitioning logic).  The reference has no multi-GPU path; this module is the
-partition the W4A16 path shards along.
+all-gather of the outputs along the last dimension at the layer boundary.  On GPUs
+and for M <= 16 on the skinny kernel's fast path that exchange is FUSED into the
+kernel: its epilogue stores the slice into every rank's buffer over NVLink and a
+small second kernel waits for the peers' flags (``PeerGather``, C ABI
+``blkq4_gather_*``).  Everything else all-gathers with ``torch.distributed`` (NCCL on
+GPUs; gloo in the CPU tests of the partitioning logic).  The reference has no
+multi-GPU path; this module is the partition the W4A16 path shards along.
 
 Quantization blocks never straddle a shard when the shard width is a multiple of
 ``shard_multiple(block, col_wise)``; quantizing a shard then yields exactly the
@@ -50,6 +53,54 @@ def gather_columns(local_out: torch.Tensor, group=None) -> torch.Tensor:
     return stacked.view(g, M, ns).permute(1, 0, 2).reshape(M, g * ns)
 
 
+class PeerGather:
+    """This rank's exchange block for the fused GEMM + all-gather, connected to all peers.
+
+    Collective: every rank of ``group`` must construct it at the same point.  The 64-byte IPC
+    handles travel through ``all_gather_object`` on the group; after that the data path uses no
+    collective library.
+    """
+
+    def __init__(self, max_rows: int, out_features: int, group=None):
+        from . import capi
+
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.max_rows, self.out_features = int(max_rows), int(out_features)
+        self.ctx = capi.GatherContext(self.world, self.rank, self.max_rows * self.out_features * 2)
+        handles = [None] * self.world
+        if self.world > 1:
+            dist.all_gather_object(handles, self.ctx.handle, group=group)
+        else:
+            handles[0] = self.ctx.handle
+        self.ctx.connect(handles)
+        if self.world > 1:
+            dist.barrier(group=group)  # nobody stores into a block before everybody has mapped it
+
+    def supports(self, layer, rows: int) -> bool:
+        """Shapes the fused kernel takes (the library refuses the others)."""
+        return (rows <= min(16, self.max_rows) and layer.col_wise and layer.block_size >= 64
+                and layer.in_features % 512 == 0 and layer.in_features <= 32768
+                and layer.out_features * self.world == self.out_features)
+
+    def forward(self, layer, x, out_full, flags=0):
+        """``out_full[M, N] = x[M, K] @ W^T`` with this rank computing its ``layer``'s columns."""
+        from . import capi
+
+        stream = torch.cuda.current_stream(x.device).cuda_stream
+        self.ctx.gemm(layer.block_size, layer.col_wise, x.size(0), layer.out_features, layer.in_features,
+                      x, layer.q_weights, layer.q_scales, layer.q_zp if layer.has_offsets else None,
+                      out_full, stream=stream, flags=flags)
+        return out_full
+
+    def status(self) -> int:
+        return self.ctx.status()
+
+    def close(self):
+        self.ctx.close()
+
+
 class ShardedBlkQ4Linear(nn.Module):
     """``BlkQ4Linear`` whose out_features are split over the ranks of ``process_group``.
 
@@ -58,7 +109,7 @@ class ShardedBlkQ4Linear(nn.Module):
     """
 
     def __init__(self, block_size, col_wise, scale_only, weights, bias_tensor=None, process_group=None,
-                 weights_are_local=False, gather_output=True):
+                 weights_are_local=False, gather_output=True, peer_gather=None):
         super().__init__()
         from .ms_blkq4linear import BlkQ4Linear
 
@@ -77,10 +128,25 @@ class ShardedBlkQ4Linear(nn.Module):
         self.in_features = weights.size(1)
         self.local = BlkQ4Linear(block_size, col_wise, scale_only, local)
         self.bias = bias_tensor  # full-width bias, added after the gather
+        # A PeerGather shared by the layers of a model (its buffers serve one call at a time):
+        # skinny inputs on CUDA then take the fused kernel instead of compute + NCCL all-gather.
+        self.peer_gather = peer_gather
 
-    def forward(self, input):
+    def forward(self, input, out=None):
         lead = input.shape[:-1]
-        out = self.local(input.reshape(-1, self.in_features))
+        x = input.reshape(-1, self.in_features)
+        pg = self.peer_gather
+        if (self.gather_output and pg is not None and x.is_cuda and pg.supports(self.local, x.size(0))):
+            full = out if out is not None else torch.empty(x.size(0), self.out_features, dtype=torch.float16,
+                                                           device=x.device)
+            lyr = self.local
+            flags = 1 if (lyr.early_weight_fetch and lyr._settled) else 0
+            pg.forward(lyr, x, full.view(-1, self.out_features), flags)
+            lyr._settled = True
+            if self.bias is not None:
+                full += self.bias
+            return full.view(*lead, self.out_features)
+        out = self.local(x)
         if self.gather_output:
             out = gather_columns(out, self.group)
             if self.bias is not None:

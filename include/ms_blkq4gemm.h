@@ -138,6 +138,44 @@ int blkq4_fp16_gemm_sm100(
   void* error_message);
 
 /*
+ * N-sharded layers on one box, one process per GPU: skinny GEMM (M <= 16) fused with the
+ * all-gather of the outputs.  No counterpart in the reference, which is single-GPU.
+ *
+ * Rank r holds the weight columns [r*n_shard, (r+1)*n_shard).  blkq4_gather_create allocates the
+ * rank's exchange block (the one place this library allocates device memory: 1 KB of control
+ * words plus two buffers of max_out_bytes) and returns its 64-byte CUDA IPC handle; the caller
+ * exchanges the handles of all ranks by any means (e.g. its process group) and passes them,
+ * ordered by rank, to blkq4_gather_connect.  blkq4_fp16_gemm_gather_sm100 then computes this
+ * rank's [m, n_shard] slice and delivers the complete [m, world*n_shard] result into
+ * output_ptr on EVERY rank: the kernel's epilogue stores the slice into all ranks' exchange
+ * buffers over NVLink and raises a per-rank flag; a second small kernel waits (bounded, ~1 s)
+ * for all flags and copies the gathered rows out.  All ranks must make the same sequence of
+ * calls; work that reads output_ptr must be enqueued on `stream` before the next gather call.
+ * A shape outside the skinny kernel's TMA fast path (column-wise, block >= 64, K % 512 == 0,
+ * M <= 16) is refused with an error text starting "Kernel execution failed: unsupported":
+ * compute with blkq4_fp16_gemm_sm80 and all-gather with the caller's collective instead.
+ * blkq4_gather_status synchronises `stream` and returns 0, or (0x400 | rank) of the first
+ * rank whose flag did not arrive in time.
+ */
+int blkq4_gather_create(int world, int rank, size_t max_out_bytes, void** ctx, void* ipc_handle_64_bytes,
+                        void* error_message);
+int blkq4_gather_connect(void* ctx, void const* ipc_handles_world_x_64_bytes, void* error_message);
+int blkq4_fp16_gemm_gather_sm100(
+  void* ctx,
+  int block_size,
+  bool column_wise_blocking,
+  int m, int n_shard, int k, void* stream,
+  void const* act_ptr, size_t a_size,
+  void const* weights_ptr, size_t weights_size,
+  void const* scales_ptr, size_t scales_size,
+  void const* offsets_ptr, size_t offsets_size,
+  void* output_ptr, size_t output_size,
+  unsigned flags,
+  void* error_message);
+int blkq4_gather_status(void* ctx, void* stream);
+int blkq4_gather_destroy(void* ctx);
+
+/*
  * Additions with no counterpart in the reference.  The reference reports errors
  * through a std::string*, which only a C++ caller can supply.  These three let
  * a C, ctypes, cgo or JNI caller own such an object.

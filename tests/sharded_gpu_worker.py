@@ -1,0 +1,66 @@
+"""Worker of tests/test_sharded_gpu.py (one rank per GPU, launched by torch.distributed.run):
+the fused GEMM + all-gather of an N-sharded layer must equal the unsharded layer on every
+rank, eagerly, over many epochs, and from a CUDA graph."""
+import os
+import sys
+import threading
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=dev)
+    from gemmlib_b200.ms_blkq4linear import BlkQ4Linear
+    from gemmlib_b200.sharded import PeerGather, ShardedBlkQ4Linear
+
+    K, N = 4096, 2048 * world
+    g = torch.Generator().manual_seed(0)
+    w = (torch.randn(N, K, generator=g) * 0.02).half().to(dev)
+    pg = PeerGather(16, N)
+    ok = True
+    for M, scale_only in [(1, True), (5, False), (16, True)]:
+        x = torch.randn(M, K, generator=g).half().to(dev)
+        full_layer = BlkQ4Linear(64, True, scale_only, w)
+        want = full_layer(x).float()
+        sharded = ShardedBlkQ4Linear(64, True, scale_only, w, peer_gather=pg)
+        tol = 2.0 ** -8 * max(1.0, float(want.abs().max()))
+        for it in range(6):
+            got = sharded(x)
+            torch.cuda.synchronize()
+            ok &= bool((got.float() - want).abs().max() <= tol)
+        out = torch.zeros(M, N, dtype=torch.float16, device=dev)
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=s):
+            sharded(x, out=out)
+        for it in range(4):
+            out.zero_()
+            graph.replay()
+            torch.cuda.synchronize()
+            ok &= bool((out.float() - want).abs().max() <= tol)
+        del graph
+    ok &= pg.status() == 0
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    torch.cuda.synchronize()
+    if int(flag.item()) == 1:
+        print("RANK_OK", rank, flush=True)
+    dist.barrier()
+    pg.close()
+    t = threading.Thread(target=dist.destroy_process_group, daemon=True)
+    t.start()
+    t.join(timeout=20)
+    sys.stdout.flush()
+    os._exit(0 if int(flag.item()) == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()

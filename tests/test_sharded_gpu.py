@@ -1,0 +1,77 @@
+"""GPU tests of the fused GEMM + all-gather (``blkq4_gather_*``).
+
+With one GPU the exchange degenerates to world size 1 (the kernel still stores into the
+exchange buffer, raises its flag, and the second kernel waits and copies out), which covers
+the epoch / slot / flag protocol, CUDA-graph replay included.  With two or more GPUs a
+torchrun job of two ranks checks the gathered result against the unsharded layer on both
+ranks.  Ranks never share a GPU: kernels that wait on one another must run on different
+devices."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from tests._util import ROOT, gaussian_act, gaussian_weight
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+@pytest.mark.parametrize("M,has_zp,block", [(1, False, 64), (4, True, 64), (16, False, 128)])
+def test_world_size_one_fused_gather_matches_plain(M, has_zp, block):
+    from gemmlib_b200.ms_blkq4linear import BlkQ4Linear
+    from gemmlib_b200.sharded import PeerGather
+
+    K, N = 2048, 1536
+    layer = BlkQ4Linear(block, True, not has_zp, gaussian_weight(N, K, seed=5).cuda())
+    x = gaussian_act(M, K, seed=6).cuda()
+    want = layer(x)
+    pg = PeerGather(16, N)
+    assert pg.supports(layer, M)
+    outs = []
+    for _ in range(5):  # epochs 1..5: both slots, flags compared against a moving epoch
+        full = torch.zeros(M, N, dtype=torch.float16, device="cuda")
+        pg.forward(layer, x, full)
+        outs.append(full)
+    # replay from a CUDA graph: the epoch lives in device memory, not in the captured launch
+    full_g = torch.zeros(M, N, dtype=torch.float16, device="cuda")
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=s):
+        pg.forward(layer, x, full_g)
+    for _ in range(3):
+        full_g.zero_()
+        g.replay()
+    torch.cuda.synchronize()
+    assert pg.status() == 0
+    for full in outs + [full_g]:
+        assert torch.allclose(full.float(), want.float(), rtol=0, atol=2.0 ** -8 * max(1.0, float(want.abs().max())))
+    pg.close()
+
+
+def test_unsupported_shape_is_refused_not_miscomputed():
+    from gemmlib_b200 import capi
+    from gemmlib_b200.ms_blkq4linear import BlkQ4Linear
+    from gemmlib_b200.sharded import PeerGather
+
+    layer = BlkQ4Linear(32, True, True, gaussian_weight(256, 512, seed=1).cuda())  # block 32: generic kernel
+    pg = PeerGather(16, 256)
+    assert not pg.supports(layer, 1)
+    with pytest.raises(capi.BlkQ4Error, match="unsupported"):
+        pg.forward(layer, gaussian_act(1, 512).cuda(), torch.empty(1, 256, dtype=torch.float16, device="cuda"))
+    pg.close()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_ranks_fused_gather_matches_unsharded():
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+           "--master-addr", "127.0.0.1", "--master-port", "29533",
+           os.path.join(ROOT, "tests", "sharded_gpu_worker.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert r.stdout.count("RANK_OK") == 2, r.stdout[-2000:] + r.stderr[-2000:]
