@@ -170,9 +170,9 @@ def run_reference(args):
 def workload_config(n_gpus):
     return {
         "workload": "c2 decode GEMV: M=1 K=4096 N=11008 block=64 column-wise symmetric, fp16 scales"
-                    + (f"; N-sharded x{n_gpus}: each rank owns one c2-sized shard, all-gather of outputs per layer"
-                       if n_gpus > 1 else ""),
-        "launches_per_step": LAYERS,
+                    + (f"; N-sharded x{n_gpus}: each rank owns one c2-sized shard; the all-gather of every layer's "
+                       "outputs is fused into the kernel (peer stores over NVLink + flag wait)" if n_gpus > 1 else ""),
+        "launches_per_step": LAYERS * (2 if n_gpus > 1 else 1),
         "l2": f"inputs larger than L2: a step walks {LAYERS} layers with distinct weights ({LAYERS} x 24 MB > 126 MB)",
         "parallelism": f"n-shard{n_gpus}" if n_gpus > 1 else "single",
     }
@@ -193,7 +193,7 @@ def run_ours(args):
 
     from gemmlib_b200 import capi
     from gemmlib_b200.ms_blkq4linear import BlkQ4Linear
-    from gemmlib_b200.sharded import gather_columns
+    from gemmlib_b200.sharded import PeerGather, gather_columns
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -202,7 +202,13 @@ def run_ours(args):
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the measured path")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    json_fd = None
     if world > 1:
+        # NCCL prints its version banner on stdout at the first collective.  The JSON line must
+        # be alone there: point fd 1 at stderr for the run and print the line through a saved copy.
+        sys.stdout.flush()
+        json_fd = os.dup(1)
+        os.dup2(2, 1)
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
     _log(f"process group ready, world {world}")
@@ -232,15 +238,23 @@ def run_ours(args):
     g = torch.Generator().manual_seed(0)
     a_host = torch.randn(M, K, generator=g).to(torch.float16).pin_memory()
     a_dev = a_host.to(dev)
-    outs = [torch.empty(M, N, dtype=torch.float16, device=dev) for _ in range(LAYERS)]
-    full = None
+    outs = [torch.empty(M, N * world, dtype=torch.float16, device=dev) for _ in range(LAYERS)]
+    peer = PeerGather(16, N * world) if world > 1 else None
+    shard_out = torch.empty(M, N, dtype=torch.float16, device=dev)
 
     def step_resident():
-        nonlocal full
         for lyr, o in zip(layers, outs):
-            lyr(a_dev, out=o)
             if world > 1:
-                full = gather_columns(o)
+                peer.forward(lyr, a_dev, o, flags=1 if lyr._settled else 0)  # fused GEMV + all-gather
+                lyr._settled = True
+            else:
+                lyr(a_dev, out=o)
+
+    def step_nccl():
+        """The unfused variant, for the extra line only: kernel, then NCCL all-gather."""
+        for lyr in layers:
+            lyr(a_dev, out=shard_out)
+            gather_columns(shard_out)
 
     # ---- CUDA graph of one step ----
     stream = torch.cuda.Stream()
@@ -293,11 +307,12 @@ def run_ours(args):
     out_host = torch.empty(M, N * world, dtype=torch.float16).pin_memory()
 
     def step_e2e():
-        for lyr in layers:
+        for lyr, o in zip(layers, outs):
             x = a_host.to(dev, non_blocking=True)
-            y = lyr(x)
             if world > 1:
-                y = gather_columns(y)
+                y = peer.forward(lyr, x, o, flags=1)
+            else:
+                y = lyr(x)
             out_host.copy_(y, non_blocking=True)
 
     for _ in range(3):
@@ -326,9 +341,33 @@ def run_ours(args):
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": LAYERS * M * K * 2,
                 "d2h_bytes_per_step": LAYERS * M * N * world * 2, "steps": e2e_steps,
                 "api": "BlkQ4Linear.forward, pinned host activation in, pinned host result out, per layer"},
-        "gpu_launches": args.steps * LAYERS,
+        "gpu_launches": args.steps * LAYERS * (2 if world > 1 else 1),
         "kernel_status": status,
     }
+    if world > 1:
+        # same layers, unfused: skinny kernel + NCCL all-gather per layer, graph replay
+        for _ in range(2):
+            step_nccl()
+        torch.cuda.synchronize()
+        g2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g2, stream=stream):
+            step_nccl()
+        for _ in range(3):
+            g2.replay()
+        barrier()
+        e0.record()
+        for _ in range(min(args.steps, 200)):
+            g2.replay()
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        nccl_ms = float(t.item())
+        line["unfused_nccl_all_gather"] = {
+            "value": round(nbytes * LAYERS * min(args.steps, 200) * world / (nccl_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
+            "us_per_layer": round(nccl_ms * 1e3 / (min(args.steps, 200) * LAYERS), 3)}
+        line["gather_status"] = peer.status()
+        del g2
     if rank == 0:
         sampler_summary = None
         time.sleep(0.15)
@@ -355,7 +394,10 @@ def run_ours(args):
         line["cpu_baseline"] = {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port",
                                 "sample": f"one c2 layer, {passes} passes of oracle dequantize+GEMV, median {sec * 1e3:.1f} ms per pass"}
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        if json_fd is not None:
+            os.write(json_fd, (json.dumps(line) + "\n").encode())
+        else:
+            print(json.dumps(line), flush=True)
     if world > 1:
         # Tear down in order: the captured graph holds NCCL kernels, so it goes first.  A
         # communicator teardown that does not return (seen with graph-captured collectives)
@@ -363,6 +405,7 @@ def run_ours(args):
         del graph
         torch.cuda.synchronize()
         dist.barrier()
+        peer.close()
         t = threading.Thread(target=dist.destroy_process_group, daemon=True)
         t.start()
         t.join(timeout=20)

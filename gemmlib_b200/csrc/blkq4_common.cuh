@@ -34,11 +34,13 @@ std::string launch_gemv(int block, bool colwise, int M, int N, int K, cudaStream
 //   [0]   uint32 epoch      layer calls completed by this rank
 //   [4]   uint32 done_ctr   CTAs of the running call that have finished storing
 //   [8]   int    error      first wait that expired (0 = none)
+//   [12]  uint32 tickets    CTAs of the wait kernel started so far (kGatherWaitCtas per call)
 //   [64]  uint32 flags[2][kGatherMaxRanks]   flags[slot][src] = epoch whose slice from `src` landed
 //   [kGatherCtrlBytes]  gathered[2][buf_bytes]  the [M, N_total] results of even / odd epochs
 constexpr int kGatherMaxRanks = 8;
 constexpr int kGatherCtrlBytes = 1024;
-constexpr int kGatherEpochOff = 0, kGatherDoneOff = 4, kGatherErrorOff = 8, kGatherFlagsOff = 64;
+constexpr int kGatherEpochOff = 0, kGatherDoneOff = 4, kGatherErrorOff = 8, kGatherTicketOff = 12, kGatherFlagsOff = 64;
+constexpr int kGatherWaitCtas = 8;  // fixed grid of the wait kernel: its call number is tickets / 8
 
 struct GatherTable {
   uint8_t* base[kGatherMaxRanks];  // every rank's block; base[rank] is the local one

@@ -5,8 +5,9 @@
 //   1. the skinny kernel, whose epilogue stores this rank's [M, N/g] columns straight into
 //      EVERY rank's gathered buffer over NVLink (plain peer stores; no multicast, no pulls) and
 //      whose last CTA raises this rank's flag in every rank's block;
-//   2. a small kernel that waits - bounded - until the flags of all ranks carry the call's
-//      epoch, then copies the complete [M, N] result into the caller's output tensor.
+//   2. a small kernel, resident alongside the first, that waits - bounded - until the flags of
+//      all ranks carry the call's epoch, then copies the complete [M, N] result into the
+//      caller's output tensor.
 // Everything a launch needs to know about "which call is this" lives in device memory (the
 // epoch word), so the pair can be captured in a CUDA graph and replayed.
 //
@@ -49,15 +50,21 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
 }
 
 // Waits until every rank's flag of this call's slot has reached the call's epoch, then copies
-// the gathered result out.  One wait per CTA (each CTA copies its own part afterwards).
+// the gathered result out.  Launched with programmatic stream serialization: its CTAs become
+// resident while the skinny kernel of the same call still runs, so the flags are seen the moment
+// they land and neither a launch gap nor a grid-completion round trip sits between the last
+// store and the copy-out.  It therefore cannot read the call's epoch from the kernel it overlaps:
+// it numbers itself, each CTA drawing a ticket (fixed grid of kGatherWaitCtas, tickets of
+// consecutive calls cannot interleave because the next skinny kernel starts only after every
+// CTA here has passed launch_dependents).
 __global__ void __launch_bounds__(256)
 gather_wait_copy_kernel(uint8_t* local, int world, unsigned long long buf_bytes, uint4* out, unsigned long long n16) {
-  // the next kernel of the stream may become resident while this one waits
-  asm volatile("griddepcontrol.launch_dependents;");
-  __shared__ int s_fail;
-  if (threadIdx.x == 0) s_fail = 0;
+  __shared__ unsigned s_epoch;
+  if (threadIdx.x == 0)
+    s_epoch = atomicAdd(reinterpret_cast<unsigned*>(local + kGatherTicketOff), 1u) / kGatherWaitCtas + 1u;
   __syncthreads();
-  const unsigned epoch = *reinterpret_cast<volatile unsigned*>(local + kGatherEpochOff);
+  asm volatile("griddepcontrol.launch_dependents;");
+  const unsigned epoch = s_epoch;
   const unsigned slot = epoch & 1u;
   if ((int)threadIdx.x < world) {
     const unsigned* flag = reinterpret_cast<const unsigned*>(local + kGatherFlagsOff) + slot * kGatherMaxRanks + threadIdx.x;
@@ -65,9 +72,9 @@ gather_wait_copy_kernel(uint8_t* local, int world, unsigned long long buf_bytes,
     while ((int)(ld_acquire_sys(flag) - epoch) < 0) {
       if (clock64() - t0 > kGatherWaitCycles) {
         atomicCAS(reinterpret_cast<int*>(local + kGatherErrorOff), 0, 0x400 | (int)threadIdx.x);
-        s_fail = 1;
         break;
       }
+      __nanosleep(64);
     }
   }
   __syncthreads();
@@ -174,9 +181,17 @@ extern "C" int blkq4_fp16_gemm_gather_sm100(void* ctx, int block_size, bool colu
       has_offsets ? reinterpret_cast<const uint8_t*>(offsets_ptr) : nullptr, gt, flags);
   if (!e.empty()) return blkq4::fail(err, "Kernel execution failed: " + e);
   const unsigned long long n16 = output_size / 16;
-  const int ctas = (int)((n16 + 255) / 256 < 32 ? (n16 + 255) / 256 : 32);
-  blkq4::gather_wait_copy_kernel<<<ctas, 256, 0, stream>>>(c->base[c->rank], c->world, c->buf_bytes,
-                                                           reinterpret_cast<uint4*>(output_ptr), n16);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(blkq4::kGatherWaitCtas);
+  cfg.blockDim = dim3(256);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, blkq4::gather_wait_copy_kernel, c->base[c->rank], c->world,
+                     (unsigned long long)c->buf_bytes, reinterpret_cast<uint4*>(output_ptr), n16);
   const cudaError_t ce = cudaGetLastError();
   if (ce != cudaSuccess) return blkq4::fail(err, std::string("Kernel execution failed: ") + cudaGetErrorString(ce));
   return 0;

@@ -622,14 +622,16 @@ gemv_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
     }
     if (ok && cur_lt >= 0) flush(cur_lt);
     if (p.gt.world > 0 && ok) {
-      // Publish: every storing thread fences its peer stores to system scope; the last consumer
-      // warp of the CTA counts the CTA in; the last CTA of the grid advances the local epoch and
-      // raises this rank's flag in every rank's block.
-      __threadfence_system();
+      // Publish.  A chain of release / acquire links, each at the narrowest scope that spans it:
+      // storing lanes -> lane 0 of their warp (__syncwarp), warps -> the CTA's last warp (fence +
+      // shared counter, CTA scope), CTAs -> the grid's last CTA (system fence + global counter),
+      // which advances the local epoch and raises this rank's flag in every rank's block.  Only
+      // one thread per CTA pays for a system-scope fence: 16 per CTA cost ~12 us per launch.
       __syncwarp();
+      if (lane == 0) __threadfence_block();
       if (lane == 0 && atomicAdd(s_done, 1) == kCons - 1) {
         uint8_t* local = p.gt.base[p.gt.rank];
-        __threadfence();
+        __threadfence_system();
         const unsigned arrived = atomicAdd(reinterpret_cast<unsigned*>(local + kGatherDoneOff), 1u);
         if (arrived == gridDim.x - 1) {
           __threadfence_system();
