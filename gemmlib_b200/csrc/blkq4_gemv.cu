@@ -275,8 +275,8 @@ gemv_kernel(const __half* __restrict__ a, const uint8_t* __restrict__ packed,
 // bounds the bytes in flight per SM (~70 KB: enough to cover HBM latency) - measured on B200,
 // asking for a whole launch's bytes up front makes every later small load (activations,
 // scales) queue behind them for microseconds.  Eight consumer warps take units round-robin,
-// release slots through "empty" mbarriers, and add their partial sums of a tile into a
-// shared accumulator; the warp that completes a tile converts and stores it.
+// release slots through "empty" mbarriers, and leave their partial sums of a tile in shared
+// memory; the warp that completes a tile adds them in a fixed order, converts and stores.
 //
 // Math side.  Scaling is moved out of the per-weight work.  A packed word x gives, with one
 // shift and four lop3, the half2 operands
@@ -305,7 +305,7 @@ constexpr int kCons = 16;                           // consumer warps
 // Parity waits on an mbarrier are only valid one phase at a time, so every slot must be
 // produced by one thread (lane = slot) and consumed by one warp (slot % kCons).
 static_assert(kRing <= 32 && kRing % kCons == 0, "slot ownership");
-constexpr int kAccBufs = 8;                         // rotating per-tile accumulators
+constexpr int kAccBufsMax = 4;                      // rotating per-tile sets of per-warp partial sums
 constexpr int kPersistThreads = (kCons + 1) * 32;
 constexpr int kCtrlBytes = 1024;                    // barriers + flags + counters
 constexpr long long kGemvWaitCycles = 2000000000ll;
@@ -346,17 +346,18 @@ gemv_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   constexpr int MR = 8 * MT;          // activation rows the mma sees (rows >= M repeat row M-1)
   constexpr int CW = HAS_ZP ? 2 : 1;  // correction floats per (step, row)
   constexpr int VALS = MT * 4;
+  constexpr int kAccBufs = MT == 1 ? kAccBufsMax : 2;  // 8 KB (MT = 1) or 16 KB (MT = 2) each
   const int total_steps = p.K >> 6;
 
   // control block: full[kRing], empty[kRing] mbarriers, abort flag, tile counters / generations
   const uint32_t bar_full = smem_u32(s_raw), bar_empty = bar_full + 8 * kRing;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(s_raw + 16 * kRing);
   int* s_cnt = reinterpret_cast<int*>(s_raw + 16 * kRing + 16);        // [kAccBufs] arrivals
-  volatile int* s_gen = reinterpret_cast<volatile int*>(s_cnt + kAccBufs);  // [kAccBufs] tiles finalized
-  int* s_done = const_cast<int*>(s_gen) + kAccBufs;                          // consumer warps finished (gather)
+  volatile int* s_gen = reinterpret_cast<volatile int*>(s_cnt + kAccBufsMax);  // [kAccBufs] tiles finalized
+  int* s_done = const_cast<int*>(s_gen) + kAccBufsMax;                          // consumer warps finished (gather)
   uint8_t* s_ring = s_raw + kCtrlBytes;
-  float* s_acc = reinterpret_cast<float*>(s_ring + kRing * kSlotBytes);   // [kAccBufs][VALS][32]
-  float* s_corr = s_acc + kAccBufs * VALS * 32;                            // [steps][MR][CW]
+  float* s_acc = reinterpret_cast<float*>(s_ring + kRing * kSlotBytes);   // [kAccBufs][kCons][VALS][32]
+  float* s_corr = s_acc + kAccBufs * kCons * VALS * 32;                            // [steps][MR][CW]
   __half* s_a = reinterpret_cast<__half*>(s_corr + total_steps * MR * CW); // [M][K] if a_smem
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -374,11 +375,10 @@ gemv_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       mbar_init(bar_empty + 8 * i, 1);
     }
     *abort_flag = 0;
-    for (int i = 0; i < kAccBufs; ++i) { s_cnt[i] = 0; s_gen[i] = 0; }
+    for (int i = 0; i < kAccBufsMax; ++i) { s_cnt[i] = 0; s_gen[i] = 0; }
     *s_done = 0;
     mbar_init_fence();
   }
-  for (int i = threadIdx.x; i < kAccBufs * VALS * 32; i += blockDim.x) s_acc[i] = 0.0f;
   __syncthreads();
 
   if (warp == kCons) {
@@ -480,11 +480,12 @@ gemv_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       gather_off = kGatherCtrlBytes + (size_t)(gather_epoch & 1u) * p.gt.buf_bytes;
     }
 
-    // Adds this warp's partial sums of local tile `lt` to the tile's shared accumulator; the
-    // warp that completes the tile rounds to fp16, stores, and recycles the accumulator.
+    // Leaves this warp's partial sums of local tile `lt` in its own slot of the tile's buffer;
+    // the warp that arrives last adds the slots up in a fixed order (the result does not depend
+    // on which warp came last), rounds to fp16, stores, and recycles the buffer.
     auto flush = [&](int lt) {
       const int b = lt % kAccBufs;
-      // the accumulator's previous tile (lt - kAccBufs) must have been finalized
+      // the buffer's previous tile (lt - kAccBufs) must have been finalized
       if (lane == 0) {
         const long long t0 = clock64();
         while (s_gen[b] != lt / kAccBufs) {
@@ -496,11 +497,11 @@ gemv_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
         }
       }
       __syncwarp();
-      float* acc = s_acc + b * VALS * 32;
+      float* buf = s_acc + b * (kCons * VALS * 32);
 #pragma unroll
       for (int j = 0; j < MT; ++j)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) atomicAdd(&acc[(j * 4 + e) * 32 + lane], total[j][e]);
+        for (int e = 0; e < 4; ++e) buf[(warp * VALS + j * 4 + e) * 32 + lane] = total[j][e];
       __syncwarp();
       int last = 0;
       if (lane == 0) {
@@ -511,17 +512,29 @@ gemv_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       if (last) {
         __threadfence_block();
         const int tile = blockIdx.x + lt * gridDim.x;
+        float sum[MT][4];
+#pragma unroll
+        for (int j = 0; j < MT; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) sum[j][e] = 0.0f;
+        // contributors: the warps of the tile's first `expected` units, in unit order
+        const int w0 = (lt * p.nsub) % kCons;
+        for (int c = 0; c < expected; ++c) {
+          const float* src = buf + ((w0 + c) % kCons) * (VALS * 32);
+#pragma unroll
+          for (int j = 0; j < MT; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sum[j][e] += src[(j * 4 + e) * 32 + lane];
+        }
 #pragma unroll
         for (int j = 0; j < MT; ++j)
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float sum = acc[(j * 4 + e) * 32 + lane];
-            acc[(j * 4 + e) * 32 + lane] = 0.0f;
             // accumulator element e of a lane: row n = g + 8 (e >> 1), column m = 8 j + 2 t + (e & 1)
             const int n = tile * 16 + g + 8 * (e >> 1);
             const int m = 8 * j + 2 * t + (e & 1);
             if (m < p.M) {
-              const __half h = __float2half_rn(sum);
+              const __half h = __float2half_rn(sum[j][e]);
               if (p.gt.world > 0) {
                 // this rank's columns of the gathered [M, n_total] result, in every rank's buffer
                 const size_t off = gather_off + ((size_t)m * p.gt.n_total + (size_t)p.gt.rank * p.N + n) * sizeof(__half);
@@ -654,6 +667,9 @@ static int env_int(const char* name) {
   return v ? atoi(v) : 0;
 }
 
+constexpr size_t kMaxDynamicSmem = 227 * 1024;
+const char* const kTooMuchSmem = "shared memory";
+
 template <int MT, bool HAS_ZP>
 std::string launch_persistent_T(int M, int N, int K, int block, cudaStream_t stream, const __half* a,
                                 const uint8_t* packed, const __half* scales, const uint8_t* zp,
@@ -686,9 +702,11 @@ std::string launch_persistent_T(int M, int N, int K, int block, cudaStream_t str
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   }
   const int grid = p.tiles < sms ? p.tiles : sms;
-  const size_t smem = kCtrlBytes + (size_t)kRing * kSlotBytes + (size_t)kAccBufs * MT * 4 * 32 * sizeof(float) +
+  const size_t smem = kCtrlBytes + (size_t)kRing * kSlotBytes +
+                      (size_t)(MT == 1 ? kAccBufsMax : 2) * kCons * MT * 4 * 32 * sizeof(float) +
                       (size_t)(K / 64) * 8 * MT * (HAS_ZP ? 2 : 1) * sizeof(float) +
                       (p.a_smem ? (size_t)M * K * 2 : 0);
+  if (smem > kMaxDynamicSmem) return kTooMuchSmem;  // very long K with 9..16 rows: the generic kernel takes it
   auto kern = gemv_persistent_kernel<MT, HAS_ZP>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return std::string(cudaGetErrorString(e));
@@ -752,11 +770,12 @@ std::string launch_gemv(int block, bool colwise, int M, int N, int K, cudaStream
   // pointers 16-byte aligned (TMA), shared memory for the per-step terms within reach.
   if (colwise && block >= 64 && !env_generic && K % kUnitKBytes == 0 && K <= 32768 &&
       reinterpret_cast<uintptr_t>(scales) % 16 == 0 && (!zp || reinterpret_cast<uintptr_t>(zp) % 16 == 0)) {
-    if (M <= 8)
-      return zp ? launch_persistent_T<1, true>(M, N, K, block, stream, a, packed, scales, zp, out, bias, early)
-                : launch_persistent_T<1, false>(M, N, K, block, stream, a, packed, scales, zp, out, bias, early);
-    return zp ? launch_persistent_T<2, true>(M, N, K, block, stream, a, packed, scales, zp, out, bias, early)
-              : launch_persistent_T<2, false>(M, N, K, block, stream, a, packed, scales, zp, out, bias, early);
+    const std::string r =
+        (M <= 8) ? (zp ? launch_persistent_T<1, true>(M, N, K, block, stream, a, packed, scales, zp, out, bias, early)
+                       : launch_persistent_T<1, false>(M, N, K, block, stream, a, packed, scales, zp, out, bias, early))
+                 : (zp ? launch_persistent_T<2, true>(M, N, K, block, stream, a, packed, scales, zp, out, bias, early)
+                       : launch_persistent_T<2, false>(M, N, K, block, stream, a, packed, scales, zp, out, bias, early));
+    if (r != kTooMuchSmem) return r;
   }
   // Row-wise blocking carries 48 bytes of meta per chunk in registers, so it fetches
   // fewer steps at a time.
@@ -783,11 +802,12 @@ std::string launch_gemv_gather(int block, bool colwise, int M, int N, int K, cud
         reinterpret_cast<uintptr_t>(scales) % 16 == 0 && (!zp || reinterpret_cast<uintptr_t>(zp) % 16 == 0)))
     return "unsupported: the fused gather runs on the column-wise block >= 64 fast path only";
   const bool early = (flags & BLKQ4_GEMM_EARLY_WEIGHT_FETCH) != 0;
-  if (M <= 8)
-    return zp ? launch_persistent_T<1, true>(M, N, K, block, stream, a, packed, scales, zp, nullptr, nullptr, early, &gt)
-              : launch_persistent_T<1, false>(M, N, K, block, stream, a, packed, scales, zp, nullptr, nullptr, early, &gt);
-  return zp ? launch_persistent_T<2, true>(M, N, K, block, stream, a, packed, scales, zp, nullptr, nullptr, early, &gt)
-            : launch_persistent_T<2, false>(M, N, K, block, stream, a, packed, scales, zp, nullptr, nullptr, early, &gt);
+  const std::string r =
+      (M <= 8) ? (zp ? launch_persistent_T<1, true>(M, N, K, block, stream, a, packed, scales, zp, nullptr, nullptr, early, &gt)
+                     : launch_persistent_T<1, false>(M, N, K, block, stream, a, packed, scales, zp, nullptr, nullptr, early, &gt))
+               : (zp ? launch_persistent_T<2, true>(M, N, K, block, stream, a, packed, scales, zp, nullptr, nullptr, early, &gt)
+                     : launch_persistent_T<2, false>(M, N, K, block, stream, a, packed, scales, zp, nullptr, nullptr, early, &gt));
+  return r == kTooMuchSmem ? std::string("unsupported: K too long for the fused gather at this M") : r;
 }
 
 }  // namespace blkq4

@@ -95,11 +95,12 @@ def test_gaussian_tolerance(block, colwise, has_zp, M):
 
 
 # Shapes that walk the streaming skinny kernel's corners: more tiles than SMs, fewer tiles than
-# SMs, a last chunk of K that is partial (K % 1024 != 0), fewer items per tile than consumer
-# warps (K < 4096), 9..16 rows, the largest meta box (K / block = 256).
+# SMs, K not a multiple of 1024, fewer units per tile than consumer warps (K < 8192), 9..16
+# rows, very long K.
 STREAM_CASES = [
     (64, False, 1, 4736, 1024), (64, True, 3, 2400, 1280), (128, False, 8, 160, 3072),
     (128, True, 16, 4768, 2048), (64, True, 9, 2432, 5120), (64, False, 2, 1600, 16384),
+    (128, True, 16, 64, 32768),  # per-step terms would not fit in shared memory: generic kernel
 ]
 
 
