@@ -383,9 +383,13 @@ def run_ours(args):
             "traffic": TRAFFIC_BYTES_PER_LAUNCH, "kernel": "gemv_persistent_kernel<1,false>",
             "bytes_per_launch": nbytes, "us_per_launch": round(launch_us, 3), "peak_source": peaks["source"],
         }
-    if world == 1:
+    if world == 1 and not args.skip_extras:
         line["quant_prepack"] = bench_quant(torch, dev, peaks)
         line["gemm"] = bench_gemm_c3(torch, dev, peaks)
+        try:
+            line["c5_stack"] = bench_c5_stack(torch, dev, peaks)
+        except Exception as exc:
+            line["c5_stack"] = {"unavailable": "%s: %s" % (type(exc).__name__, exc)}
         try:
             line["reference_gpu"] = bench_reference_gpu(torch, dev, layers, a_dev)
         except Exception as exc:  # a baseline must never cost the measurement
@@ -415,9 +419,9 @@ def run_ours(args):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the timed kernel, from the
-# committed ncu capture (profiles/gemv_persistent_c2.md): 23,988,736 B read, 0 B written
+# committed ncu capture (profiles/gemv_persistent_c2.md): 24,025,344 B read, 0 B written
 # (the 22 KB of output stay in L2 within the captured launch).
-TRAFFIC_BYTES_PER_LAUNCH = 23988736
+TRAFFIC_BYTES_PER_LAUNCH = 24025344
 
 
 def bench_quant(torch, dev, peaks):
@@ -542,6 +546,46 @@ def bench_reference_gpu(torch, dev, layers_c2, a_dev):
     return out
 
 
+def bench_c5_stack(torch, dev, peaks):
+    """configs[4]: the 224 linears of a Llama-2-7B-shaped decoder (32 x {q,k,v,o: 4096->4096;
+    gate,up: 4096->11008; down: 11008->4096}), block 64 with zero points, random weights,
+    replayed as one CUDA graph by LinearStack: decode (M=1, HBM roofline) and prefill (M=512,
+    tensor roofline)."""
+    from gemmlib_b200.stack import llama_like_stack
+
+    gen = torch.Generator(device=dev).manual_seed(5)
+
+    def weight_fn(n, k):
+        return (torch.randn(n, k, generator=gen, device=dev) * 0.02).to(torch.float16)
+
+    st = llama_like_stack(4096, 11008, 32, 64, True, False, dev, weight_fn=weight_fn)
+    out = {"workload": "c5: 224 linears (32 Llama-2-7B-shaped blocks), block 64 zero points, one CUDA graph per M",
+           "linears": st.num_linears}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for M, reps in ((1, 50), (512, 10)):
+        st.buffers(M)["x"].copy_(torch.randn(M, 4096, generator=gen, device=dev).to(torch.float16))
+        for _ in range(3):
+            st.replay(M)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            st.replay(M)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        nbytes = sum(algorithmic_bytes(M, l.in_features, l.out_features, 64, True, True) for l, _, _ in st.steps)
+        flops = sum(2.0 * M * l.in_features * l.out_features for l, _, _ in st.steps)
+        if M == 1:
+            gbs = nbytes / (ms * 1e-3) / 1e9
+            out["decode_M1"] = {"ms_per_pass": round(ms, 4), "GB/s": round(gbs, 1),
+                                "frac_of_hbm": round(gbs / peaks["hbm_gbs"], 4), "bytes_per_pass": nbytes}
+        else:
+            tf = flops / (ms * 1e-3) / 1e12
+            out["prefill_M512"] = {"ms_per_pass": round(ms, 4), "TFLOP/s": round(tf, 1),
+                                   "frac_of_tensor": round(tf / peaks["tflops"], 4)}
+    return out
+
+
 def bench_gemm_c3(torch, dev, peaks):
     """Prefill GEMM (configs[2]) through BlkQ4Linear.forward: TFLOP/s against the tensor roofline."""
     from gemmlib_b200.ms_blkq4linear import BlkQ4Linear
@@ -620,6 +664,8 @@ def main():
     ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-extras", action="store_true",
+                    help="headline workload only (no quantize / GEMM / stack / baseline lines): for profiler runs")
     ap.add_argument("--profile", choices=["gemv", "gemm", "quant"], default=None,
                     help="profiling driver: a few plain launches of one kernel (see profiles/)")
     ap.add_argument("--launches", type=int, default=8)
