@@ -25,6 +25,8 @@ SYMBOLS = (
     "blkq4_last_kernel_status",
     "blkq4_gather_create",
     "blkq4_gather_connect",
+    "blkq4_gather_local_block",
+    "blkq4_gather_connect_pointers",
     "blkq4_fp16_gemm_gather_sm100",
     "blkq4_gather_status",
     "blkq4_gather_destroy",
@@ -64,6 +66,10 @@ def _load() -> ctypes.CDLL:
     lib.blkq4_gather_create.restype = i
     lib.blkq4_gather_connect.argtypes = [vp, vp, vp]
     lib.blkq4_gather_connect.restype = i
+    lib.blkq4_gather_local_block.argtypes = [vp]
+    lib.blkq4_gather_local_block.restype = vp
+    lib.blkq4_gather_connect_pointers.argtypes = [vp, ctypes.POINTER(vp), vp]
+    lib.blkq4_gather_connect_pointers.restype = i
     lib.blkq4_fp16_gemm_gather_sm100.argtypes = [vp, i, b, i, i, i, vp, vp, sz, vp, sz, vp, sz, vp, sz, vp, sz,
                                                  ctypes.c_uint, vp]
     lib.blkq4_fp16_gemm_gather_sm100.restype = i
@@ -180,6 +186,16 @@ class GatherContext:
             raise ValueError("need one 64-byte handle per rank")
         with _ErrMsg() as e:
             if lib.blkq4_gather_connect(self._ctx, blob, e.p) != 0:
+                raise BlkQ4Error(e.text())
+
+    def local_block(self) -> int:
+        return int(lib.blkq4_gather_local_block(self._ctx) or 0)
+
+    def connect_pointers(self, blocks):
+        """Single process, several contexts: ``blocks[r]`` = ``local_block()`` of rank r's context."""
+        arr = (ctypes.c_void_p * self.world)(*[ctypes.c_void_p(b) for b in blocks])
+        with _ErrMsg() as e:
+            if lib.blkq4_gather_connect_pointers(self._ctx, arr, e.p) != 0:
                 raise BlkQ4Error(e.text())
 
     def gemm(self, block_size, column_wise, m, n_shard, k, act, q_weights, q_scales, q_zp, out_full, stream=0,

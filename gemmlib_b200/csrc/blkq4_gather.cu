@@ -135,6 +135,22 @@ extern "C" int blkq4_gather_connect(void* ctx, void const* handles, void* err) {
   return 0;
 }
 
+extern "C" void* blkq4_gather_local_block(void* ctx) {
+  auto* c = reinterpret_cast<GatherCtx*>(ctx);
+  return c ? c->base[c->rank] : nullptr;
+}
+
+extern "C" int blkq4_gather_connect_pointers(void* ctx, void* const* blocks, void* err) {
+  auto* c = reinterpret_cast<GatherCtx*>(ctx);
+  if (!c || !blocks) return blkq4::fail(err, "Null argument");
+  for (int r = 0; r < c->world; ++r) {
+    if (r == c->rank) continue;
+    if (!blocks[r]) return blkq4::fail(err, "Null block pointer for rank " + std::to_string(r));
+    c->base[r] = reinterpret_cast<uint8_t*>(blocks[r]);  // not opened by this context: not closed by it
+  }
+  return 0;
+}
+
 extern "C" int blkq4_fp16_gemm_gather_sm100(void* ctx, int block_size, bool column_wise_blocking, int m,
                                             int n_shard, int k, void* stream_ptr, void const* act_ptr,
                                             size_t a_size, void const* weights_ptr, size_t weights_size,

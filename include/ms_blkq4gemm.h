@@ -160,6 +160,10 @@ int blkq4_fp16_gemm_sm100(
 int blkq4_gather_create(int world, int rank, size_t max_out_bytes, void** ctx, void* ipc_handle_64_bytes,
                         void* error_message);
 int blkq4_gather_connect(void* ctx, void const* ipc_handles_world_x_64_bytes, void* error_message);
+/* One process driving several GPUs (peer access enabled by the caller) connects its contexts
+ * with plain pointers instead of IPC handles: blocks[r] = blkq4_gather_local_block(ctx of rank r). */
+void* blkq4_gather_local_block(void* ctx);
+int blkq4_gather_connect_pointers(void* ctx, void* const* blocks_by_rank, void* error_message);
 int blkq4_fp16_gemm_gather_sm100(
   void* ctx,
   int block_size,

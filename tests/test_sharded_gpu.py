@@ -66,6 +66,33 @@ def test_unsupported_shape_is_refused_not_miscomputed():
     pg.close()
 
 
+def test_missing_peer_expires_the_bounded_wait_and_reports_it():
+    """Failure detection without a GPU fault: rank 0 of a two-rank exchange runs, rank 1 never
+    does (its flag is a word nothing sets).  The wait kernel gives up after its ~1 s limit,
+    records (0x400 | rank 1), and the context, the stream and the device stay usable."""
+    from gemmlib_b200 import capi
+    from gemmlib_b200.ms_blkq4linear import BlkQ4Linear
+
+    K, ns = 1024, 256
+    layer = BlkQ4Linear(64, True, True, gaussian_weight(ns, K, seed=2).cuda())
+    x = gaussian_act(1, K, seed=3).cuda()
+    a = capi.GatherContext(2, 0, 16 * 2 * ns * 2)
+    b = capi.GatherContext(2, 1, 16 * 2 * ns * 2)   # exists, is mapped, never runs
+    blocks = [a.local_block(), b.local_block()]
+    a.connect_pointers(blocks)
+    b.connect_pointers(blocks)
+    out = torch.zeros(1, 2 * ns, dtype=torch.float16, device="cuda")
+    a.gemm(64, True, 1, ns, K, x, layer.q_weights, layer.q_scales, None, out)
+    assert a.status() == (0x400 | 1)
+    # rank 0's own half arrived in its buffer and was copied out; the device still works
+    want = layer(x)
+    torch.cuda.synchronize()
+    assert torch.allclose(out[:, :ns].float(), want.float(), atol=2.0 ** -8 * max(1.0, float(want.abs().max())), rtol=0)
+    assert capi.last_kernel_status() == 0
+    a.close()
+    b.close()
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_ranks_fused_gather_matches_unsharded():
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
