@@ -17,6 +17,8 @@ LIB_PATH = os.path.join(_PKG, "libms_blkq4gemm.so")
 SYMBOLS = (
     "blkq4_fp16_gemm_sm80",
     "blkq4_fp16_gemm_sm100",
+    "blkq4_fp16_gemm_ws_sm100",
+    "blkq4_gemm_workspace_size",
     "blkq4_fp16_quant_sm80",
     "blkq4_fp16_quant_size_sm80",
     "blkq4_errmsg_create",
@@ -50,6 +52,11 @@ def _load() -> ctypes.CDLL:
     lib.blkq4_fp16_gemm_sm80.restype = i
     lib.blkq4_fp16_gemm_sm100.argtypes = [i, b, i, i, i, vp, vp, sz, vp, sz, vp, sz, vp, sz, vp, sz, vp, sz, ctypes.c_uint, vp]
     lib.blkq4_fp16_gemm_sm100.restype = i
+    lib.blkq4_fp16_gemm_ws_sm100.argtypes = [i, b, i, i, i, vp, vp, sz, vp, sz, vp, sz, vp, sz, vp, sz, vp, sz,
+                                             ctypes.c_uint, vp, sz, vp]
+    lib.blkq4_fp16_gemm_ws_sm100.restype = i
+    lib.blkq4_gemm_workspace_size.argtypes = [i, i, i]
+    lib.blkq4_gemm_workspace_size.restype = sz
     lib.blkq4_fp16_quant_sm80.argtypes = [i, b, i, i, i, vp, vp, sz, vp, sz, vp, sz, vp, sz, vp]
     lib.blkq4_fp16_quant_sm80.restype = i
     i64p = ctypes.POINTER(ctypes.c_int64)  # int64_t& is passed as a pointer
@@ -142,7 +149,13 @@ def quant(block_size, column_wise, rows, columns, ld, weights, q_weights, q_scal
 EARLY_WEIGHT_FETCH = 1  # BLKQ4_GEMM_EARLY_WEIGHT_FETCH
 
 
-def gemm(block_size, column_wise, m, n, k, act, q_weights, q_scales, q_zp, out, stream=0, flags=0, bias=None):
+def gemm_workspace_size(m: int, n: int, k: int) -> int:
+    """Bytes of zeroed workspace with which the tensor-core kernel would split K (0: it would not)."""
+    return int(lib.blkq4_gemm_workspace_size(m, n, k))
+
+
+def gemm(block_size, column_wise, m, n, k, act, q_weights, q_scales, q_zp, out, stream=0, flags=0, bias=None,
+         workspace=None):
     """Without ``flags`` and ``bias`` calls the reference-named entry point, otherwise
     ``blkq4_fp16_gemm_sm100``."""
     ap, as_ = _ptr_size(act)
@@ -151,8 +164,14 @@ def gemm(block_size, column_wise, m, n, k, act, q_weights, q_scales, q_zp, out, 
     zp, zs = _ptr_size(q_zp)
     op, os_ = _ptr_size(out)
     bp, bs = _ptr_size(bias)
+    wp, ws = _ptr_size(workspace)
     with _ErrMsg() as e:
-        if flags or bs:
+        if ws:
+            rc = lib.blkq4_fp16_gemm_ws_sm100(
+                block_size, column_wise, m, n, k, stream, ap, as_, qp, qs, sp, ss, zp, zs, op, os_, bp, bs, flags,
+                wp, ws, e.p
+            )
+        elif flags or bs:
             rc = lib.blkq4_fp16_gemm_sm100(
                 block_size, column_wise, m, n, k, stream, ap, as_, qp, qs, sp, ss, zp, zs, op, os_, bp, bs, flags, e.p
             )

@@ -93,13 +93,13 @@ extern "C" int blkq4_fp16_quant_sm80(int block_size, bool column_wise_blocking, 
   return 0;
 }
 
-extern "C" int blkq4_fp16_gemm_sm100(int block_size, bool column_wise_blocking, int m, int n, int k,
-                                     void* stream_ptr, void const* act_ptr, size_t a_size,
-                                     void const* weights_ptr, size_t weights_size,
-                                     void const* scales_ptr, size_t scales_size,
-                                     void const* offsets_ptr, size_t offsets_size, void* output_ptr,
-                                     size_t output_size, void const* bias_ptr, size_t bias_size,
-                                     unsigned flags, void* err) {
+extern "C" int blkq4_fp16_gemm_ws_sm100(int block_size, bool column_wise_blocking, int m, int n, int k,
+                                        void* stream_ptr, void const* act_ptr, size_t a_size,
+                                        void const* weights_ptr, size_t weights_size,
+                                        void const* scales_ptr, size_t scales_size,
+                                        void const* offsets_ptr, size_t offsets_size, void* output_ptr,
+                                        size_t output_size, void const* bias_ptr, size_t bias_size,
+                                        unsigned flags, void* workspace, size_t workspace_size, void* err) {
   if (!blkq4::supported_block(block_size))
     return fail(err, "Unsupported block size: " + std::to_string(block_size));
   if (m <= 0 || n <= 0 || k <= 0)
@@ -159,9 +159,28 @@ extern "C" int blkq4_fp16_gemm_sm100(int block_size, bool column_wise_blocking, 
   // kernel from the tcgen05 tensor-core kernel.
   const std::string e =
       (m <= 16) ? blkq4::launch_gemv(block_size, column_wise_blocking, m, n, k, stream, a, w, s, z, o, bias, flags)
-                : blkq4::launch_gemm_tc(block_size, column_wise_blocking, m, n, k, stream, a, w, s, z, o, bias);
+                : blkq4::launch_gemm_tc(block_size, column_wise_blocking, m, n, k, stream, a, w, s, z, o, bias, workspace,
+                                          workspace_size);
   if (!e.empty()) return fail(err, "Kernel execution failed: " + e);
   return 0;
+}
+
+extern "C" int blkq4_fp16_gemm_sm100(int block_size, bool column_wise_blocking, int m, int n, int k,
+                                     void* stream_ptr, void const* act_ptr, size_t a_size,
+                                     void const* weights_ptr, size_t weights_size,
+                                     void const* scales_ptr, size_t scales_size,
+                                     void const* offsets_ptr, size_t offsets_size, void* output_ptr,
+                                     size_t output_size, void const* bias_ptr, size_t bias_size,
+                                     unsigned flags, void* err) {
+  return blkq4_fp16_gemm_ws_sm100(block_size, column_wise_blocking, m, n, k, stream_ptr, act_ptr, a_size,
+                                  weights_ptr, weights_size, scales_ptr, scales_size, offsets_ptr,
+                                  offsets_size, output_ptr, output_size, bias_ptr, bias_size, flags, nullptr,
+                                  0, err);
+}
+
+extern "C" size_t blkq4_gemm_workspace_size(int m, int n, int k) {
+  if (m <= 0 || n <= 0 || k <= 0 || (k % 64) != 0) return 0;
+  return blkq4::gemm_tc_workspace_bytes(m, n, k);
 }
 
 extern "C" int blkq4_fp16_gemm_sm80(int block_size, bool column_wise_blocking, int m, int n, int k,

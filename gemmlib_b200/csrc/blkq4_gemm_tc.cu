@@ -81,6 +81,13 @@ struct Params {
   uint32_t meta_row_bytes_s, meta_row_bytes_z;  // bytes per box row
   __half* out;
   const __half* bias;  // fp16 [N] added to the fp16 result, or null
+  // Split-K: a work item is (tile, part) with part < split covering k_per_item steps; parts
+  // 0 .. split-2 leave fp32 partial tiles in the workspace, the last part adds them to its own.
+  int split_shift;     // log2(split), split in {1, 2, 4}
+  int k_per_item;      // 64-k steps per work item
+  int num_items;       // tiles << split_shift
+  float* ws_partials;  // [tile][split-1][BM][128] fp32
+  unsigned* ws_flags;  // [tile] arrivals (self-resetting)
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
@@ -222,8 +229,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
   auto bar = [&](int id) { return bars + 8u * (uint32_t)id; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int num_tiles = p.m_tiles * p.n_tiles;
-  const int k_steps = p.K / BLOCK_K;
   const uint32_t tmem_cols = p.tmem_cols;
 
   if (threadIdx.x == 0) {
@@ -258,9 +263,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     // Stage sa = it % kActStages is free once the commit group of step it - kActStages retired.
     if (lane == 0) {
       uint32_t it = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < p.num_items; item += gridDim.x) {
+        const int tile = item >> p.split_shift;
         const int m_tile = tile % p.m_tiles;
-        for (int ks = 0; ks < k_steps; ++ks, ++it) {
+        const int ks0 = (item - (tile << p.split_shift)) * p.k_per_item;
+        for (int ks = ks0; ks < ks0 + p.k_per_item; ++ks, ++it) {
           const int sa = it % kActStages;
           if (it >= (uint32_t)kActStages) {
             const uint32_t g = (it - kActStages) / kCommitSteps;  // commit group of the stage's last user
@@ -280,9 +287,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       const uint32_t tx = kPackTileBytes + (uint32_t)p.meta_rows * p.meta_row_bytes_s +
                           (p.has_zp ? (uint32_t)p.meta_rows * p.meta_row_bytes_z : 0u);
       uint32_t it = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < p.num_items; item += gridDim.x) {
+        const int tile = item >> p.split_shift;
         const int n_tile = tile / p.m_tiles;
-        for (int ks = 0; ks < k_steps; ++ks, ++it) {
+        const int ks0 = (item - (tile << p.split_shift)) * p.k_per_item;
+        for (int ks = ks0; ks < ks0 + p.k_per_item; ++ks, ++it) {
           const int s = it % kStages;
           if (it >= (uint32_t)kStages &&
               !mbar_wait(bar(BAR_PACK_FREE + s), ((it / kStages) - 1) & 1, abort_flag, 0x110 | s))
@@ -324,13 +333,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       const uint32_t a_tmem0 = tmem_base + (uint32_t)p.a_col0;
       uint32_t s = 0, sa = 0, par_s = 0, par_sa = 0, gdone = 0, it = 0, tcount = 0;
       uint32_t ab = 0, par_acc = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
+      for (int item = blockIdx.x; item < p.num_items; item += gridDim.x, ++tcount) {
         if (tcount >= (uint32_t)p.acc_bufs &&
             !mbar_wait(bar(BAR_ACC_EMPTY + ab), par_acc ^ 1u, abort_flag, 0x200 | ab))
           goto mma_done;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + ab * (uint32_t)p.BM;
-        for (int ks = 0; ks < k_steps; ++ks, ++it) {
+        for (int ks = 0; ks < p.k_per_item; ++ks, ++it) {
           const uint32_t bar_a = bar(BAR_ACT_FULL) + 8u * sa, bar_d = bar(BAR_DEQ_FULL) + 8u * s;
           if (!mbar_try_wait(bar_a, par_sa) && !mbar_wait(bar_a, par_sa, abort_flag, 0x210 | sa)) goto mma_done;
           if (!mbar_try_wait(bar_d, par_s) && !mbar_wait(bar_d, par_s, abort_flag, 0x220 | s)) goto mma_done;
@@ -357,11 +366,56 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     // consecutive n, i.e. 64 contiguous bytes of the row-major output.
     const int quarter = warp & 3;
     uint32_t tcount = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
+    const int split = 1 << p.split_shift;
+    const size_t tile_floats = (size_t)p.BM * TILE_N;
+    for (int item = blockIdx.x; item < p.num_items; item += gridDim.x, ++tcount) {
+      const int tile = item >> p.split_shift, part = item - (tile << p.split_shift);
       const int n_tile = tile / p.m_tiles, m_tile = tile % p.m_tiles;
       const int ab = tcount % p.acc_bufs;
       if (!mbar_wait(bar(BAR_ACC_FULL + ab), (tcount / p.acc_bufs) & 1, abort_flag, 0x300 | ab)) break;
       tc_fence_after();
+      const int n_l = quarter * 32 + lane;
+      if (part < split - 1) {
+        // ---- split-K, not the last part: fp32 partial tile [m][n] to the workspace: for a row m
+        //      the 32 lanes of a warp write 128 contiguous bytes.  (One line per lane, [n][m] with
+        //      16-byte accesses, was measured slower: 32 lines touched per instruction.)
+        float* dst_ws = p.ws_partials + ((size_t)tile * (split - 1) + part) * tile_floats + n_l;
+        const int rows = min(p.BM, p.M - m_tile * p.BM);
+        for (int c0 = 0; c0 < rows; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(ab * p.BM + c0), r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (c0 + j < rows) dst_ws[(size_t)(c0 + j) * TILE_N] = __uint_as_float(r[j]);
+        }
+        tc_fence_before();
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(bar(BAR_ACC_EMPTY + ab));
+          atomicAdd(p.ws_flags + tile, 1u);
+        }
+        continue;
+      }
+      if (split > 1) {
+        // ---- split-K, last part: wait (bounded) for the other parts' partial tiles ----
+        if (lane == 0) {
+          const unsigned want = (unsigned)((split - 1) * kNumEpiWarps);
+          const long long t0 = clock64();
+          while (*reinterpret_cast<volatile unsigned*>(p.ws_flags + tile) < want) {
+            if (*abort_flag || clock64() - t0 > kWaitCycles) {
+              *abort_flag = 1;
+              atomicCAS(&g_gemm_tc_error, 0, 0x320 | quarter);
+              break;
+            }
+          }
+          __threadfence();
+        }
+        __syncwarp();
+        if (*abort_flag) break;
+      }
+      const float* src_ws = p.ws_partials + (size_t)tile * (split - 1) * tile_floats + n_l;
       const int n = n_tile * TILE_N + quarter * 32 + lane;
       const int m0 = m_tile * p.BM;
       // Lanes pair up (n even / odd) so that every store carries two adjacent n (4 bytes per
@@ -374,6 +428,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(ab * p.BM + c0), r);
         tmem_ld_wait();
+        if (split > 1) {
+          // add the other parts in part order (a fixed order: the result is reproducible)
+          for (int q = 0; q < split - 1; ++q) {
+            const float* sq = src_ws + (size_t)q * tile_floats + (size_t)c0 * TILE_N;
+            float f[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = (m0 + c0 + j < p.M) ? __ldcg(sq + (size_t)j * TILE_N) : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + f[j]);
+          }
+        }
         int m = m0 + c0 + odd;
         __half* dst = p.out + (size_t)m * p.N + (n & ~1);
         // The bias is added to the ROUNDED result in fp16, which is what a separate
@@ -395,7 +460,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(BAR_ACC_EMPTY + ab));
+      if (lane == 0) {
+        mbar_arrive(bar(BAR_ACC_EMPTY + ab));
+        // the warp that completes the tile's count puts the flag back to zero for the next launch
+        if (split > 1 && atomicAdd(p.ws_flags + tile, 1u) == (unsigned)(split * kNumEpiWarps - 1)) p.ws_flags[tile] = 0u;
+      }
     }
   } else if (warp < kWeightProducerWarp) {
     // =============================== dequantizers ===============================
@@ -413,9 +482,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     const int np_l = 8 * (n_l >> 4) + (n_l & 7);
     const uint32_t nib_shift = (n_l & 8) ? 8u : 0u;
     const uint32_t tmem_row = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)p.a_col0;
-    int my_tiles = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) ++my_tiles;
-    const uint32_t total_its = (uint32_t)my_tiles * (uint32_t)k_steps;
+    int my_items = 0;
+    for (int item = blockIdx.x; item < p.num_items; item += gridDim.x) ++my_items;
+    const uint32_t total_its = (uint32_t)my_items * (uint32_t)p.k_per_item;
     for (uint32_t it = group; it < total_its; it += kDeqGroups) {
       const int s = it % kStages, d = it % kDeqStages;
       if (it >= (uint32_t)kDeqStages) {
@@ -508,9 +577,56 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
 
 }  // namespace
 
+namespace {
+
+int sm_count() {
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return sms;
+}
+
+// Split-K plan.  The kernel is persistent with one CTA per SM, so a problem with few output
+// tiles (prefill of a 4096-wide layer at M = 512: 64 tiles on 148 SMs) leaves SMs idle; cutting
+// every tile's K range in `split` work items fills them.
+struct SplitPlan {
+  int split_shift;
+  size_t flags_bytes, total_bytes;  // workspace: [flags, 256-byte aligned][partials]
+};
+
+SplitPlan plan_split(int M, int N, int K, size_t ws_bytes_available) {
+  const int BM = M >= 256 ? 256 : ((M + 15) / 16) * 16;
+  const int tiles = ((M + BM - 1) / BM) * ((N + TILE_N - 1) / TILE_N);
+  const int k_steps = K / BLOCK_K;
+  const int sms = sm_count() > 0 ? sm_count() : 148;
+  SplitPlan best{0, 0, 0};
+  // Split only when every work item still gets an SM of its own (one round): measured on B200 a
+  // second round of half-size items loses more to the fp32 exchange than it gains in balance.
+  for (int shift = 1; shift <= 2; ++shift) {
+    const int split = 1 << shift;
+    if (k_steps % split != 0 || k_steps / split < 8 || tiles * split > sms) continue;
+    const size_t flags = ((size_t)tiles * sizeof(unsigned) + 255) & ~(size_t)255;
+    const size_t total = flags + (size_t)tiles * (split - 1) * BM * TILE_N * sizeof(float);
+    if (total > ws_bytes_available) continue;
+    best = SplitPlan{shift, flags, total};
+  }
+  return best;
+}
+
+}  // namespace
+
+size_t gemm_tc_workspace_bytes(int M, int N, int K) {
+  if (M <= 16) return 0;
+  return plan_split(M, N, K, ~(size_t)0).total_bytes;
+}
+
 std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
                            const __half* a, const uint8_t* packed, const __half* scales,
-                           const uint8_t* zp, __half* out, const __half* bias) {
+                           const uint8_t* zp, __half* out, const __half* bias, void* workspace,
+                           size_t workspace_bytes) {
   Params p{};
   p.M = M; p.N = N; p.K = K; p.block = block;
   p.block_shift = block == 16 ? 4 : block == 32 ? 5 : block == 64 ? 6 : 7;
@@ -553,11 +669,16 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
   }
   if (!ok) return "cuTensorMapEncodeTiled failed";
 
-  int dev = 0, sms = 0;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int sms = sm_count();
   const int num_tiles = p.m_tiles * p.n_tiles;
-  const int grid = num_tiles < sms ? num_tiles : sms;
+  const SplitPlan sp = (workspace && reinterpret_cast<uintptr_t>(workspace) % 256 == 0)
+                           ? plan_split(M, N, K, workspace_bytes) : SplitPlan{0, 0, 0};
+  p.split_shift = sp.split_shift;
+  p.k_per_item = (K / BLOCK_K) >> sp.split_shift;
+  p.num_items = num_tiles << sp.split_shift;
+  p.ws_flags = reinterpret_cast<unsigned*>(workspace);
+  p.ws_partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + sp.flags_bytes);
+  const int grid = p.num_items < sms ? p.num_items : sms;
   const SmemPlan plan = make_plan(p.BM);
   auto kern = colwise ? gemm_tc_kernel<true> : gemm_tc_kernel<false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.total);

@@ -61,7 +61,8 @@ std::vector<torch::Tensor> blkq4linear_quant(int block_size, bool col_wise, bool
 torch::Tensor blkq4linear_forward_out(int block_size, bool col_wise, int in_features, int out_features,
                                       torch::Tensor input, torch::Tensor q_weights, torch::Tensor q_scales,
                                       torch::Tensor q_zp, torch::Tensor output,
-                                      c10::optional<torch::Tensor> bias, int64_t flags) {
+                                      c10::optional<torch::Tensor> bias, int64_t flags,
+                                      c10::optional<torch::Tensor> workspace) {
   TORCH_CHECK(input.scalar_type() == torch::kFloat16, "blkq4linear_forward only supports float16 inputs");
   TORCH_CHECK(input.dim() == 2 && input.size(1) == in_features,
               "Activation shape is not compatible with the weights");
@@ -84,14 +85,20 @@ torch::Tensor blkq4linear_forward_out(int block_size, bool col_wise, int in_feat
   const c10::cuda::CUDAGuard guard(dev);
   const bool has_zp = q_zp.defined() && q_zp.numel() > 0;
   std::string err;
-  int rc = blkq4_fp16_gemm_sm100(block_size, col_wise, int(input.size(0)), out_features, in_features,
+  const bool has_ws = workspace.has_value() && workspace->defined() && workspace->numel() > 0;
+  if (has_ws)
+    TORCH_CHECK(workspace->device() == dev && workspace->is_contiguous(),
+                "The split-K workspace must be a contiguous tensor on the input's device");
+  int rc = blkq4_fp16_gemm_ws_sm100(block_size, col_wise, int(input.size(0)), out_features, in_features,
                                  c10::cuda::getCurrentCUDAStream().stream(), input.data_ptr(),
                                  size_t(input.numel()) * kHalfBytes, q_weights.data_ptr(),
                                 size_t(q_weights.numel()), q_scales.data_ptr(),
                                 size_t(q_scales.numel()) * kHalfBytes, has_zp ? q_zp.data_ptr() : nullptr,
                                 has_zp ? size_t(q_zp.numel()) : 0, output.data_ptr(),
                                 size_t(output.numel()) * kHalfBytes, has_bias ? bias->data_ptr() : nullptr,
-                                has_bias ? size_t(bias->numel()) * kHalfBytes : 0, unsigned(flags), &err);
+                                has_bias ? size_t(bias->numel()) * kHalfBytes : 0, unsigned(flags),
+                                has_ws ? workspace->data_ptr() : nullptr,
+                                has_ws ? size_t(workspace->numel()) * workspace->element_size() : 0, &err);
   TORCH_CHECK(rc == 0, err);
   return output;
 }
@@ -103,7 +110,7 @@ torch::Tensor blkq4linear_forward(int block_size, bool col_wise, int in_features
   auto output = torch::empty({input.size(0), out_features},
                              torch::TensorOptions().dtype(torch::kFloat16).device(input.device()));
   return blkq4linear_forward_out(block_size, col_wise, in_features, out_features, input, q_weights, q_scales,
-                                 q_zp, output, c10::nullopt, 0);
+                                 q_zp, output, c10::nullopt, 0, c10::nullopt);
 }
 
 }  // namespace
@@ -114,7 +121,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("forward_out", &blkq4linear_forward_out, "Forward pass into a caller-provided output tensor",
         py::arg("block_size"), py::arg("col_wise"), py::arg("in_features"), py::arg("out_features"),
         py::arg("input"), py::arg("q_weights"), py::arg("q_scales"), py::arg("q_zp"), py::arg("output"),
-        py::arg("bias") = py::none(), py::arg("flags") = 0);
+        py::arg("bias") = py::none(), py::arg("flags") = 0, py::arg("workspace") = py::none());
+  m.def("gemm_workspace_size", [](int m_, int n_, int k_) { return int64_t(blkq4_gemm_workspace_size(m_, n_, k_)); },
+        "Bytes of zeroed workspace with which the tensor-core kernel splits K (0: it does not)");
   m.attr("EARLY_WEIGHT_FETCH") = int(BLKQ4_GEMM_EARLY_WEIGHT_FETCH);
   m.def("library_version", []() { return std::string(blkq4_version()); });
 }

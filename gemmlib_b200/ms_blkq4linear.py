@@ -14,7 +14,9 @@ into a caller's tensor; a float16 bias on the layer's device is added inside the
 epilogue (bit-identical to the reference's separate ``output += bias``, one pass over the
 output less); and, from the second call on, the skinny kernel is launched with
 ``BLKQ4_GEMM_EARLY_WEIGHT_FETCH`` (set ``early_weight_fetch = False`` on a layer whose
-packed tensors are rewritten by work queued on the same stream as ``forward``).
+packed tensors are rewritten by work queued on the same stream as ``forward``); prefill
+shapes with too few output tiles to fill the GPU split K through a workspace shared per
+(device, stream) (``split_k = False`` turns that off).
 """
 from __future__ import annotations
 
@@ -22,6 +24,23 @@ import torch
 from torch import nn
 
 from . import ms_blkq4linear_ext
+
+
+# Split-K workspaces: one zero-initialised buffer per (device, stream), shared by all layers (calls
+# on one stream run one at a time; the kernel leaves the buffer's flags zeroed).  Grown on demand.
+_WORKSPACES = {}
+
+
+def split_k_workspace(device, nbytes: int):
+    if nbytes <= 0:
+        return None
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 16 << 20), dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = ws
+    return ws
 
 
 class BlkQ4Linear(nn.Module):
@@ -40,6 +59,7 @@ class BlkQ4Linear(nn.Module):
         self.register_buffer("q_zp", q_zp)
         self.bias = bias_tensor
         self.early_weight_fetch = True
+        self.split_k = True  # prefill shapes with few output tiles split K through a shared workspace
         self._settled = False  # the first forward is a plain launch, ordered after the quantizer
 
     @classmethod
@@ -58,6 +78,7 @@ class BlkQ4Linear(nn.Module):
         self.register_buffer("q_zp", q_zp)
         self.bias = bias_tensor
         self.early_weight_fetch = True
+        self.split_k = True  # prefill shapes with few output tiles split K through a shared workspace
         self._settled = False
         return self
 
@@ -81,9 +102,13 @@ class BlkQ4Linear(nn.Module):
             output = out.view(-1, self.out_features)
         fused = self._fusable_bias(x)
         flags = ms_blkq4linear_ext.EARLY_WEIGHT_FETCH if (self.early_weight_fetch and self._settled) else 0
+        ws = None
+        if x.size(0) > 16 and self.split_k:
+            ws = split_k_workspace(x.device, ms_blkq4linear_ext.gemm_workspace_size(
+                x.size(0), self.out_features, self.in_features))
         ms_blkq4linear_ext.forward_out(
             self.block_size, self.col_wise, self.in_features, self.out_features,
-            x, self.q_weights, self.q_scales, self.q_zp, output, fused, flags)
+            x, self.q_weights, self.q_scales, self.q_zp, output, fused, flags, ws)
         self._settled = True
         if self.bias is not None and fused is None:
             output += self.bias

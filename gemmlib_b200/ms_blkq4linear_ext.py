@@ -30,3 +30,4 @@ forward = _mod.forward
 forward_out = _mod.forward_out
 library_version = _mod.library_version
 EARLY_WEIGHT_FETCH = _mod.EARLY_WEIGHT_FETCH
+gemm_workspace_size = _mod.gemm_workspace_size

@@ -137,6 +137,32 @@ int blkq4_fp16_gemm_sm100(
   unsigned flags,
   void* error_message);
 
+/**
+ * blkq4_fp16_gemm_sm100 with a caller-owned workspace: device memory of at least
+ * blkq4_gemm_workspace_size(m, n, k) bytes, 256-byte aligned, ZERO-INITIALISED once (the kernel
+ * leaves it zeroed), used by one call at a time (calls on one stream may share it).  With it the
+ * tensor-core kernel splits K when the output has too few 128 x 256 tiles to fill the GPU's SMs
+ * (e.g. M = 512, N = 4096: 64 tiles on 148 SMs): parts of a tile's K range run on different SMs,
+ * leave fp32 partial tiles in the workspace and the last part adds them in a fixed order.  A
+ * null or too small workspace, or a size query of 0, means the call runs exactly as
+ * blkq4_fp16_gemm_sm100.  No counterpart in the reference (its split-K template parameters
+ * are unused, src/mickey/blk_q4/f16_gemm_sm80.h:86-90).
+ */
+size_t blkq4_gemm_workspace_size(int m, int n, int k);
+int blkq4_fp16_gemm_ws_sm100(
+  int block_size,
+  bool column_wise_blocking,
+  int m, int n, int k, void* stream,
+  void const* act_ptr, size_t a_size,
+  void const* weights_ptr, size_t weights_size,
+  void const* scales_ptr, size_t scales_size,
+  void const* offsets_ptr, size_t offsets_size,
+  void* output_ptr, size_t output_size,
+  void const* bias_ptr, size_t bias_size,
+  unsigned flags,
+  void* workspace, size_t workspace_size,
+  void* error_message);
+
 /*
  * N-sharded layers on one box, one process per GPU: skinny GEMM (M <= 16) fused with the
  * all-gather of the outputs.  No counterpart in the reference, which is single-GPU.

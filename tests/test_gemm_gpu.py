@@ -21,13 +21,13 @@ def to_cuda(a):
     return None if a is None else torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
-def gpu_gemm(block, colwise, a_mk, N, packed, scales, zp, flags=0):
+def gpu_gemm(block, colwise, a_mk, N, packed, scales, zp, flags=0, workspace=None):
     from gemmlib_b200 import capi
 
     M, K = a_mk.shape
     a, pw, ps, pz = to_cuda(a_mk), to_cuda(packed), to_cuda(scales), to_cuda(zp)
     out = torch.full((M, N), float("nan"), dtype=torch.float16, device="cuda")
-    capi.gemm(block, colwise, M, N, K, a, pw, ps, pz, out, flags=flags)
+    capi.gemm(block, colwise, M, N, K, a, pw, ps, pz, out, flags=flags, workspace=workspace)
     torch.cuda.synchronize()
     assert capi.last_kernel_status() == 0
     return out.cpu().numpy()
@@ -63,11 +63,11 @@ def test_every_m_class_exact(M):
         assert (bits(got) == bits(want)).all(), (M, block, colwise, has_zp, N, K)
 
 
-def check_gaussian(block, colwise, has_zp, M, N, K, sigma=0.02, flags=0):
+def check_gaussian(block, colwise, has_zp, M, N, K, sigma=0.02, flags=0, workspace=None):
     w = gaussian_weight(N, K, sigma=sigma, seed=K + N)
     a = gaussian_act(M, K, seed=M).numpy()
     pw, ps, pz = O.quant_prepack(block, colwise, w.numpy(), has_zp)
-    got = gpu_gemm(block, colwise, a, N, pw, ps, pz, flags=flags).astype(np.float64)
+    got = gpu_gemm(block, colwise, a, N, pw, ps, pz, flags=flags, workspace=workspace).astype(np.float64)
     assert np.isfinite(got).all()
     wdq = O.dequant(block, colwise, K, N, pw, ps, pz)
     want = O.gemm(a, wdq).astype(np.float64)
@@ -163,6 +163,44 @@ def test_fused_bias_equals_separate_add(case):
     assert torch.equal(plain.view(torch.int16), fused.view(torch.int16))
     with pytest.raises(capi.BlkQ4Error, match="bias"):
         capi.gemm(block, colwise, M, N, K, a, pw, ps, pz, fused, bias=bias[:-2])
+
+
+@pytest.mark.parametrize("case", [(64, True, True, 512, 512, 2048), (32, False, False, 300, 384, 1024),
+                                  (128, True, False, 48, 1024, 4096), (16, True, True, 700, 256, 1024)],
+                         ids=lambda c: "-".join(map(str, c)))
+def test_split_k_with_workspace(case):
+    """blkq4_fp16_gemm_ws_sm100: few output tiles, so K is split over several SMs through the
+    caller's workspace.  Same parity bars as the unsplit kernel; the flags part of the workspace
+    is back to zero afterwards; two runs agree bit for bit (partials are added in part order)."""
+    from gemmlib_b200 import capi
+
+    block, colwise, has_zp, M, N, K = case
+    need = capi.gemm_workspace_size(M, N, K)
+    assert need > 0, "the shape is meant to split"
+    ws = torch.zeros(need, dtype=torch.uint8, device="cuda")
+    check_gaussian(block, colwise, has_zp, M, N, K, workspace=ws)
+    tiles = -(-M // min(256, -(-M // 16) * 16)) * -(-N // 128)
+    assert int(ws[: 4 * tiles].view(torch.int32).abs().sum()) == 0
+    w = gaussian_weight(N, K, seed=K + N)
+    a = gaussian_act(M, K, seed=M).numpy()
+    pw, ps, pz = O.quant_prepack(block, colwise, w.numpy(), has_zp)
+    r1 = gpu_gemm(block, colwise, a, N, pw, ps, pz, workspace=ws)
+    r2 = gpu_gemm(block, colwise, a, N, pw, ps, pz, workspace=ws)
+    assert (bits(r1) == bits(r2)).all()
+    # a workspace that is too small is ignored, not an error
+    small = torch.zeros(256, dtype=torch.uint8, device="cuda")
+    r3 = gpu_gemm(block, colwise, a, N, pw, ps, pz, workspace=small)
+    plain = gpu_gemm(block, colwise, a, N, pw, ps, pz)
+    assert (bits(r3) == bits(plain)).all()
+
+
+def test_split_k_is_not_planned_for_full_grids():
+    from gemmlib_b200 import capi
+
+    assert capi.gemm_workspace_size(2048, 4096, 4096) == 0   # 256 tiles on 148 SMs: nothing idle
+    assert capi.gemm_workspace_size(512, 11008, 4096) == 0   # 172 tiles: a second round would cost more
+    assert capi.gemm_workspace_size(16, 4096, 4096) == 0     # skinny kernel
+    assert capi.gemm_workspace_size(512, 4096, 4096) > 0
 
 
 def test_config_c1_cpu_reference_case():
