@@ -19,6 +19,8 @@ SYMBOLS = (
     "blkq4_fp16_gemm_sm100",
     "blkq4_fp16_gemm_ws_sm100",
     "blkq4_gemm_workspace_size",
+    "blkq4_fp16_gemm_static_ws_sm100",
+    "blkq4_static_scratch_size",
     "blkq4_fp16_quant_sm80",
     "blkq4_fp16_quant_size_sm80",
     "blkq4_errmsg_create",
@@ -57,6 +59,10 @@ def _load() -> ctypes.CDLL:
     lib.blkq4_fp16_gemm_ws_sm100.restype = i
     lib.blkq4_gemm_workspace_size.argtypes = [i, i, i]
     lib.blkq4_gemm_workspace_size.restype = sz
+    lib.blkq4_fp16_gemm_static_ws_sm100.argtypes = [i, b, i, i, i, vp, vp, sz, vp, sz, vp, sz, vp, sz, vp, sz, vp, sz,
+                                                    ctypes.c_uint, vp]
+    lib.blkq4_fp16_gemm_static_ws_sm100.restype = i
+    lib.blkq4_static_scratch_size.restype = sz
     lib.blkq4_fp16_quant_sm80.argtypes = [i, b, i, i, i, vp, vp, sz, vp, sz, vp, sz, vp, sz, vp]
     lib.blkq4_fp16_quant_sm80.restype = i
     i64p = ctypes.POINTER(ctypes.c_int64)  # int64_t& is passed as a pointer
@@ -152,6 +158,27 @@ EARLY_WEIGHT_FETCH = 1  # BLKQ4_GEMM_EARLY_WEIGHT_FETCH
 def gemm_workspace_size(m: int, n: int, k: int) -> int:
     """Bytes of zeroed workspace with which the tensor-core kernel would split K (0: it would not)."""
     return int(lib.blkq4_gemm_workspace_size(m, n, k))
+
+
+def static_scratch_size() -> int:
+    return int(lib.blkq4_static_scratch_size())
+
+
+def gemm_static_ws(block_size, column_wise, m, n, k, act, q_weights, q_scales, q_zp, out, stream=0, flags=0,
+                   bias=None):
+    """``blkq4_fp16_gemm_static_ws_sm100``: split-K with the library's own device scratch array."""
+    ap, as_ = _ptr_size(act)
+    qp, qs = _ptr_size(q_weights)
+    sp, ss = _ptr_size(q_scales)
+    zp, zs = _ptr_size(q_zp)
+    op, os_ = _ptr_size(out)
+    bp, bs = _ptr_size(bias)
+    with _ErrMsg() as e:
+        rc = lib.blkq4_fp16_gemm_static_ws_sm100(
+            block_size, column_wise, m, n, k, stream, ap, as_, qp, qs, sp, ss, zp, zs, op, os_, bp, bs, flags, e.p
+        )
+        if rc != 0:
+            raise BlkQ4Error(e.text())
 
 
 def gemm(block_size, column_wise, m, n, k, act, q_weights, q_scales, q_zp, out, stream=0, flags=0, bias=None,

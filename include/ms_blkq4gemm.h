@@ -163,6 +163,27 @@ int blkq4_fp16_gemm_ws_sm100(
   void* workspace, size_t workspace_size,
   void* error_message);
 
+/**
+ * blkq4_fp16_gemm_ws_sm100 with the workspace taken from a 12 MiB device array that is part of the
+ * library (blkq4_static_scratch_size() bytes) instead of from the caller: nothing on this path
+ * allocates, on the host or on the device.  A problem whose split-K workspace
+ * (blkq4_gemm_workspace_size) would not fit is refused with an error; one call at a time per
+ * device may use the array.  No counterpart in the reference.
+ */
+size_t blkq4_static_scratch_size(void);
+int blkq4_fp16_gemm_static_ws_sm100(
+  int block_size,
+  bool column_wise_blocking,
+  int m, int n, int k, void* stream,
+  void const* act_ptr, size_t a_size,
+  void const* weights_ptr, size_t weights_size,
+  void const* scales_ptr, size_t scales_size,
+  void const* offsets_ptr, size_t offsets_size,
+  void* output_ptr, size_t output_size,
+  void const* bias_ptr, size_t bias_size,
+  unsigned flags,
+  void* error_message);
+
 /*
  * N-sharded layers on one box, one process per GPU: skinny GEMM (M <= 16) fused with the
  * all-gather of the outputs.  No counterpart in the reference, which is single-GPU.
