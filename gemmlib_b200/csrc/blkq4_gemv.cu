@@ -369,15 +369,23 @@ gemv_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
   // Lets the next kernel of the stream start as soon as every CTA of this one is resident (a
   // no-op unless that kernel was launched with programmatic stream serialization).
   asm volatile("griddepcontrol.launch_dependents;");
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < kRing; ++i) {
-      mbar_init(bar_full + 8 * i, 1);
-      mbar_init(bar_empty + 8 * i, 1);
+  // Set-up is on every launch's critical path (nothing streams before it): the producer warp
+  // initialises its own barriers, one lane per slot, and fetches the tensor maps early.
+  if (warp == kCons) {
+    if (lane < kRing) {
+      mbar_init(bar_full + 8 * lane, 1);
+      mbar_init(bar_empty + 8 * lane, 1);
     }
+    if (lane == 0) {
+      prefetch_tensormap(&tm_w);
+      prefetch_tensormap(&tm_s);
+      if (HAS_ZP) prefetch_tensormap(&tm_z);
+    }
+    mbar_init_fence();
+  } else if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int i = 0; i < kAccBufsMax; ++i) { s_cnt[i] = 0; s_gen[i] = 0; }
     *s_done = 0;
-    mbar_init_fence();
   }
   __syncthreads();
 
@@ -401,10 +409,13 @@ gemv_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
       const uint32_t fb = bar_full + 8 * slot;
       const uint32_t dst = smem_u32(s_ring + slot * kSlotBytes);
       mbar_arrive_expect_tx(fb, tx);
+      // Weights first: the lanes issue in lockstep and an SM starts one TMA copy every ~25-30 ns,
+      // so whatever comes second is queued behind 32 copies; the 4 KB of weights are what the
+      // consumers wait for, the few hundred bytes of scales catch up.
+      tma_load_2d(dst, &tm_w, sb * (kUnitKBytes / 4), tile * 8, fb);  // x in uint32 elements
       const int mrow = (sb * kUnitSteps) >> bs;
       tma_load_2d(dst + kSlotScaleOff, &tm_s, tile * 16, mrow, fb);
       if (HAS_ZP) tma_load_2d(dst + kSlotZpOff, &tm_z, tile * 16, mrow, fb);
-      tma_load_2d(dst, &tm_w, sb * (kUnitKBytes / 4), tile * 8, fb);  // x in uint32 elements
     }
   } else {
     // ================================ consumers ===============================
