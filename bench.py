@@ -387,6 +387,10 @@ def run_ours(args):
         line["quant_prepack"] = bench_quant(torch, dev, peaks)
         line["gemm"] = bench_gemm_c3(torch, dev, peaks)
         try:
+            line["c4_sweep"] = bench_c4_sweep(torch, dev, peaks)
+        except Exception as exc:
+            line["c4_sweep"] = {"unavailable": "%s: %s" % (type(exc).__name__, exc)}
+        try:
             line["c5_stack"] = bench_c5_stack(torch, dev, peaks)
         except Exception as exc:
             line["c5_stack"] = {"unavailable": "%s: %s" % (type(exc).__name__, exc)}
@@ -584,6 +588,50 @@ def bench_c5_stack(torch, dev, peaks):
             out["prefill_M512"] = {"ms_per_pass": round(ms, 4), "TFLOP/s": round(tf, 1),
                                    "frac_of_tensor": round(tf / peaks["tflops"], 4)}
     return out
+
+
+def bench_c4_sweep(torch, dev, peaks):
+    """configs[3]: K=8192, N=28672, block 128 column-wise symmetric (no reference kernel exists for
+    block 128), M from decode to prefill.  Two weight sets (2 x 117 MB > L2) alternate inside one
+    CUDA graph.  Each M is reported both ways (GB/s of algorithmic bytes and TFLOP/s) with the
+    roofline that binds it: HBM below the crossover (~M = 75), the tensor pipe above."""
+    from gemmlib_b200.ms_blkq4linear import BlkQ4Linear
+
+    K, N, block = 8192, 28672, 128
+    gen = torch.Generator(device=dev).manual_seed(7)
+    layers = [BlkQ4Linear(block, True, True, (torch.randn(N, K, generator=gen, device=dev) * 0.015).to(torch.float16))
+              for _ in range(2)]
+    rows = []
+    stream = torch.cuda.Stream()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for M in (1, 4, 16, 64, 256, 1024, 4096):
+        x = torch.randn(M, K, generator=gen, device=dev).to(torch.float16)
+        out = torch.empty(M, N, dtype=torch.float16, device=dev)
+        with torch.cuda.stream(stream):
+            for _ in range(2):
+                for lyr in layers:
+                    lyr(x, out=out)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for lyr in layers:
+                lyr(x, out=out)
+        graph.replay()
+        torch.cuda.synchronize()
+        reps = 20 if M <= 256 else 4
+        e0.record()
+        for _ in range(reps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (reps * len(layers))
+        nbytes = algorithmic_bytes(M, K, N, block, True, False)
+        gbs, tf = nbytes / us / 1e3, 2.0 * M * N * K / us / 1e6
+        t_hbm, t_tc = nbytes / (peaks["hbm_gbs"] * 1e3), 2.0 * M * N * K / (peaks["tflops"] * 1e6)
+        rows.append({"M": M, "us": round(us, 2), "GB/s": round(gbs, 1), "TFLOP/s": round(tf, 1),
+                     "bound": "hbm" if t_hbm >= t_tc else "tensor", "frac": round(max(t_hbm, t_tc) / us, 4)})
+        del graph
+    return {"workload": "c4: K=8192 N=28672 block 128 column-wise symmetric, 2 weight sets per graph", "rows": rows}
 
 
 def bench_gemm_c3(torch, dev, peaks):
