@@ -481,7 +481,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     const int n_l = 32 * (warp & 3) + lane;
     const int np_l = 8 * (n_l >> 4) + (n_l & 7);
     const uint32_t nib_shift = (n_l & 8) ? 8u : 0u;
-    const int pk_swz = (np_l >> 1) & 3;  // the tile's 64-byte swizzle: chunk c of this column is at c ^ pk_swz
     const uint32_t tmem_row = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)p.a_col0;
     int my_items = 0;
     for (int item = blockIdx.x; item < p.num_items; item += gridDim.x) ++my_items;
@@ -500,7 +499,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       uint32_t out[32];
 #pragma unroll
       for (int c = 0; c < 4; ++c) {  // 16-byte chunk: k in [16 c, 16 c + 16)
-        const uint4 wv = *reinterpret_cast<const uint4*>(pk + ((c ^ pk_swz) << 4));
+        const uint4 wv = *reinterpret_cast<const uint4*>(pk + c * 16);
         const uint32_t w4[4] = {wv.x >> nib_shift, wv.y >> nib_shift, wv.z >> nib_shift, wv.w >> nib_shift};
         // scale / offset half2 for the k pairs (2r, 2r+1) [lo] and (2r+8, 2r+9) [hi] of word r
         uint32_t s_lo[4], s_hi[4], o_lo[4], o_hi[4];
@@ -649,12 +648,12 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
   CUtensorMap tm_act, tm_pack, tm_scale, tm_zp;
   bool ok = encode_tensor_map_2d(&tm_act, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a, (uint64_t)K, (uint64_t)M, BLOCK_K,
                       (uint32_t)p.BM, CU_TENSOR_MAP_SWIZZLE_128B);
-  // 64-byte swizzle: the 16-byte chunk c of packed column r lands at chunk c ^ ((r >> 1) & 3), so the
-  // eight lanes of a quarter warp, which read the same chunk of eight consecutive columns (64 bytes
-  // apart), hit eight different bank groups instead of two (measured without it: 70 % of the
-  // dequantizers' shared-memory wavefronts were bank-conflict replays).
+  // No swizzle on the packed tile: the dequantizers' 16-byte loads of eight neighbouring packed
+  // columns (64 bytes apart) do conflict four ways, but a 64-byte TMA swizzle that removes the
+  // conflicts measured 1-2 % SLOWER on the same GPU (c3 59.2 vs 58.2 us): those loads are not on
+  // the critical path, the extra XOR per load is.
   ok = ok && encode_tensor_map_2d(&tm_pack, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, packed, (uint64_t)K, (uint64_t)(N / 2),
-                       BLOCK_K, TILE_N / 2, CU_TENSOR_MAP_SWIZZLE_64B);
+                       BLOCK_K, TILE_N / 2, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (colwise) {
     p.meta_rows = block >= BLOCK_K ? 1 : BLOCK_K / block;
     p.meta_row_bytes_s = TILE_N * 2;

@@ -264,10 +264,123 @@ quant_prepack_kernel(const __half* __restrict__ w, int K, int N, int ld, bool ve
   }
 }
 
+// Column-wise blocks, 16-byte aligned rows: one thread per 16-byte packed chunk, everything in
+// registers.  A chunk holds 16 consecutive k of columns na and na + 8, i.e. 32 contiguous bytes of
+// each of two weight rows; the BLOCK / 16 lanes that share a quantization block are neighbours in
+// the warp, so a block's range is a shuffle reduction.  No shared memory, no block-wide barrier:
+// the kernel is a stream of independent 128-bit loads and stores.  Same arithmetic as the tiled
+// kernel (range_to_scale_zp / range_to_scale / quantize_one), hence the same bits.
+template <int BLOCK>
+__global__ void __launch_bounds__(kThreads)
+quant_prepack_colwise_kernel(const __half* __restrict__ w, int K, int N, int ld, uint8_t* __restrict__ packed,
+                             __half* __restrict__ scales, uint8_t* __restrict__ zps) {
+  constexpr int G = BLOCK / 16;  // lanes per quantization block: 1, 2, 4, 8
+  const int kch = K / 16;        // chunks per packed column
+  const long long total = (long long)(N / 2) * kch;
+  const long long c_raw = (long long)blockIdx.x * kThreads + threadIdx.x;
+  const bool valid = c_raw < total;
+  const long long c = valid ? c_raw : total - 1;  // every lane stays for the shuffles
+  const int np = (int)(c / kch), kc = (int)(c - (long long)np * kch);
+  const int na = 16 * (np / 8) + (np % 8);
+  const bool has_zp = zps != nullptr;
+  const int lane = threadIdx.x & 31;
+
+  const uint4* pa = reinterpret_cast<const uint4*>(w + (size_t)na * ld + kc * 16);
+  const uint4* pb = reinterpret_cast<const uint4*>(w + (size_t)(na + 8) * ld + kc * 16);
+  uint4 va[2], vb[2];
+  va[0] = __ldg(pa);
+  va[1] = __ldg(pa + 1);
+  vb[0] = __ldg(pb);
+  vb[1] = __ldg(pb + 1);
+  const __half* ha = reinterpret_cast<const __half*>(va);
+  const __half* hb = reinterpret_cast<const __half*>(vb);
+
+  // range of the 16 values of each column (fp16 min/max are exact; NaNs are skipped as in the
+  // reference's "v < min" scan), then of the whole block across its G lanes
+  auto range16 = [](const uint4 (&v)[2], float& mn, float& mx) {
+    const __half2* h0 = reinterpret_cast<const __half2*>(&v[0]);
+    const __half2* h1 = reinterpret_cast<const __half2*>(&v[1]);
+    __half2 mn2 = __hmin2(h0[0], h1[0]), mx2 = __hmax2(h0[0], h1[0]);
+#pragma unroll
+    for (int i = 1; i < 4; ++i) {
+      mn2 = __hmin2(mn2, __hmin2(h0[i], h1[i]));
+      mx2 = __hmax2(mx2, __hmax2(h0[i], h1[i]));
+    }
+    const float2 fmn = __half22float2(mn2), fmx = __half22float2(mx2);
+    mn = fminf(fmn.x, fmn.y);
+    mx = fmaxf(fmx.x, fmx.y);
+  };
+  float mna, mxa, mnb, mxb;
+  range16(va, mna, mxa);
+  range16(vb, mnb, mxb);
+#pragma unroll
+  for (int o = 1; o < G; o <<= 1) {
+    mna = fminf(mna, __shfl_xor_sync(0xffffffffu, mna, o));
+    mxa = fmaxf(mxa, __shfl_xor_sync(0xffffffffu, mxa, o));
+    mnb = fminf(mnb, __shfl_xor_sync(0xffffffffu, mnb, o));
+    mxb = fmaxf(mxb, __shfl_xor_sync(0xffffffffu, mxb, o));
+  }
+  // first element of the block (the symmetric all-zero case keeps its sign of zero)
+  const int lead = lane & ~(G - 1);
+  const float first_a = __shfl_sync(0xffffffffu, __half2float(ha[0]), lead);
+  const float first_b = __shfl_sync(0xffffffffu, __half2float(hb[0]), lead);
+
+  __half sca, scb;
+  uint8_t zpa = 8, zpb = 8;
+  if (has_zp) {
+    range_to_scale_zp(mna, mxa, sca, zpa);
+    range_to_scale_zp(mnb, mxb, scb, zpb);
+  } else {
+    sca = range_to_scale(mna, mxa, first_a);
+    scb = range_to_scale(mnb, mxb, first_b);
+  }
+  const float sa = __half2float(sca), sb = __half2float(scb);
+  const float ra = (sa != 0.0f) ? __fdiv_rn(1.0f, sa) : 0.0f;
+  const float rb = (sb != 0.0f) ? __fdiv_rn(1.0f, sb) : 0.0f;
+  const float za = (float)zpa, zb = (float)zpb;
+
+  uint32_t qa[16], qb[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    qa[i] = quantize_one(__half2float(ha[i]), ra, za);
+    qb[i] = quantize_one(__half2float(hb[i]), rb, zb);
+  }
+  // Byte 4 row + sub = q[2 row + (sub >> 1), sub & 1 ? nb : na] | q[the same k + 8, same n] << 4
+  // (reference dev_prepack_weights, f16_quant_sm80.cuh:362-417).
+  uint32_t out[4];
+#pragma unroll
+  for (int row = 0; row < 4; ++row) {
+    out[row] = (qa[2 * row] | (qa[2 * row + 8] << 4)) |
+               ((qb[2 * row] | (qb[2 * row + 8] << 4)) << 8) |
+               ((qa[2 * row + 1] | (qa[2 * row + 9] << 4)) << 16) |
+               ((qb[2 * row + 1] | (qb[2 * row + 9] << 4)) << 24);
+  }
+  if (!valid) return;
+  *reinterpret_cast<uint4*>(packed + (size_t)np * K + kc * 16) = make_uint4(out[0], out[1], out[2], out[3]);
+  if (lane == lead) {
+    // meta row-major [K / BLOCK, N] (reference dev_prepack_scales, column-wise branch)
+    const size_t g = (size_t)((kc * 16) / BLOCK) * N + na;
+    scales[g] = sca;
+    scales[g + 8] = scb;
+    if (has_zp) {
+      zps[g] = zpa;
+      zps[g + 8] = zpb;
+    }
+  }
+}
+
 template <int BLOCK, bool COLWISE>
 void launch_T(int K, int N, int ld, cudaStream_t stream, const __half* w, uint8_t* packed,
               __half* scales, uint8_t* zp) {
   using T = QuantTile<BLOCK, COLWISE>;
+  if constexpr (COLWISE) {
+    if ((reinterpret_cast<uintptr_t>(w) % 16 == 0) && (ld % 8 == 0)) {
+      const long long total = (long long)(N / 2) * (K / 16);
+      quant_prepack_colwise_kernel<BLOCK><<<(unsigned)((total + kThreads - 1) / kThreads), kThreads, 0, stream>>>(
+          w, K, N, ld, packed, scales, zp);
+      return;
+    }
+  }
   dim3 grid(K / T::TK, (N + T::TN - 1) / T::TN);
   const bool vec_ok = (reinterpret_cast<uintptr_t>(w) % 16 == 0) && (ld % 8 == 0);
   quant_prepack_kernel<BLOCK, COLWISE>
