@@ -94,3 +94,43 @@ def test_gemm_and_quant_reject_bad_sizes_before_touching_the_device(lib_built):
         capi.quant(32, True, K, N, K, fake(2 * K * N), fake(K * N // 2), fake(2 * 2 * N), fake(1))
     with pytest.raises(capi.BlkQ4Error, match="Unexpected weight tensor size"):
         capi.quant(32, True, K, N, K, fake(10), fake(K * N // 2), fake(2 * 2 * N), None)
+
+
+def test_extension_entry_points_validate_on_the_host(lib_built):
+    """The entry points without a reference counterpart check their extra arguments before any
+    device work too: bias size, workspace planning, static scratch limit, gather arguments."""
+    import ctypes as C
+
+    from gemmlib_b200 import capi
+
+    M, N, K = 4, 32, 64
+    fake = lambda nbytes: (0x1000, nbytes)  # noqa: E731
+    with pytest.raises(capi.BlkQ4Error, match="Unexpected bias tensor size: 6 expected: 64"):
+        capi.gemm(32, True, M, N, K, fake(2 * M * K), fake(K * N // 2), fake(2 * 2 * N), None, fake(2 * M * N),
+                  bias=fake(6))
+    with pytest.raises(capi.BlkQ4Error, match="Bias tensor must be 4-byte aligned"):
+        capi.gemm(32, True, M, N, K, fake(2 * M * K), fake(K * N // 2), fake(2 * 2 * N), None, fake(2 * M * N),
+                  bias=(0x1002, 2 * N))
+    # split-K planning is a pure host function (it falls back to 148 SMs without a device)
+    assert capi.gemm_workspace_size(512, 4096, 4096) == 256 + 64 * 256 * 128 * 4
+    assert capi.gemm_workspace_size(2048, 4096, 4096) == 0
+    assert capi.gemm_workspace_size(16, 4096, 4096) == 0
+    assert capi.gemm_workspace_size(512, 4096, 512) == 0           # too few k steps per part
+    assert capi.gemm_workspace_size(512, 4096, 100) == 0           # not a GEMM shape
+    assert capi.static_scratch_size() == 12 << 20
+    with pytest.raises(capi.BlkQ4Error, match="exceeds the static scratch"):
+        capi.gemm_static_ws(64, True, 256, 4096, 4096, fake(2 * 256 * 4096), fake(4096 * 4096 // 2),
+                            fake(2 * 64 * 4096), None, fake(2 * 256 * 4096))
+    # gather: argument checks that come before any allocation
+    ctx, handle = C.c_void_p(), C.create_string_buffer(64)
+    err = capi.lib.blkq4_errmsg_create()
+    try:
+        assert capi.lib.blkq4_gather_create(9, 0, 1024, C.byref(ctx), handle, err) == -1
+        assert b"Unsupported world size" in capi.lib.blkq4_errmsg_cstr(err)
+        assert capi.lib.blkq4_gather_create(2, 2, 1024, C.byref(ctx), handle, err) == -1
+        assert capi.lib.blkq4_gather_create(2, 0, 0, C.byref(ctx), handle, err) == -1
+        assert capi.lib.blkq4_fp16_gemm_gather_sm100(None, 64, True, 1, 32, 512, None, None, 0, None, 0, None, 0,
+                                                     None, 0, None, 0, 0, err) == -1
+        assert b"Null gather context" in capi.lib.blkq4_errmsg_cstr(err)
+    finally:
+        capi.lib.blkq4_errmsg_destroy(err)
