@@ -160,7 +160,7 @@ extern "C" int blkq4_fp16_gemm_ws_sm100(int block_size, bool column_wise_blockin
   const std::string e =
       (m <= 16) ? blkq4::launch_gemv(block_size, column_wise_blocking, m, n, k, stream, a, w, s, z, o, bias, flags)
                 : blkq4::launch_gemm_tc(block_size, column_wise_blocking, m, n, k, stream, a, w, s, z, o, bias, workspace,
-                                          workspace_size);
+                                          workspace_size, flags);
   if (!e.empty()) return fail(err, "Kernel execution failed: " + e);
   return 0;
 }

@@ -31,8 +31,12 @@
 // n0 + 8 read the same 64 bytes per step and each keeps its own nibbles.  Dequantization numerics are the
 // reference kernel's (fp16(16+q) by bit trick, fma.rn.f16 with rn(scale*(-16-zp));
 // src/mickey/cutlass_ext/q4gemm/warp/quantb_meta_mma_tensor_op_tile_iterator.h:69-104, :436-543).
+#include <cstddef>
+#include <cstdint>
+
 #include "blkq4_common.cuh"
 #include "blkq4_tma.cuh"
+#include "ms_blkq4gemm.h"
 
 namespace blkq4 {
 
@@ -230,6 +234,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t tmem_cols = p.tmem_cols;
+  // Programmatic dependent launch: the next kernel of the stream may start its own set-up as soon
+  // as every CTA of this one is resident.  In this kernel only the roles that touch activations,
+  // the output or the split-K workspace wait for the preceding kernel (griddepcontrol.wait; it
+  // returns at once for a plain launch); barrier set-up, TMEM allocation, the weight copies and the
+  // dequantization of the first stages run ahead of it.
+  asm volatile("griddepcontrol.launch_dependents;");
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kActStages; ++i) mbar_init(bar(BAR_ACT_FULL + i), 1);
@@ -262,6 +272,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     // ========================= TMA producer: activations ========================
     // Stage sa = it % kActStages is free once the commit group of step it - kActStages retired.
     if (lane == 0) {
+      asm volatile("griddepcontrol.wait;" ::: "memory");  // activations belong to stream order
       uint32_t it = 0;
       for (int item = blockIdx.x; item < p.num_items; item += gridDim.x) {
         const int tile = item >> p.split_shift;
@@ -366,6 +377,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     // consecutive n, i.e. 64 contiguous bytes of the row-major output.
     const int quarter = warp & 3;
     uint32_t tcount = 0;
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // output and workspace belong to stream order
     const int split = 1 << p.split_shift;
     const size_t tile_floats = (size_t)p.BM * TILE_N;
     for (int item = blockIdx.x; item < p.num_items; item += gridDim.x, ++tcount) {
@@ -626,7 +638,7 @@ size_t gemm_tc_workspace_bytes(int M, int N, int K) {
 std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
                            const __half* a, const uint8_t* packed, const __half* scales,
                            const uint8_t* zp, __half* out, const __half* bias, void* workspace,
-                           size_t workspace_bytes) {
+                           size_t workspace_bytes, unsigned flags) {
   Params p{};
   p.M = M; p.N = N; p.K = K; p.block = block;
   p.block_shift = block == 16 ? 4 : block == 32 ? 5 : block == 64 ? 6 : 7;
@@ -687,8 +699,19 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
   auto kern = colwise ? gemm_tc_kernel<true> : gemm_tc_kernel<false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.total);
   if (e != cudaSuccess) return std::string(cudaGetErrorString(e));
-  kern<<<grid, kThreads, plan.total, stream>>>(tm_act, tm_pack, tm_scale, tm_zp, p);
-  e = cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = plan.total;
+  cfg.stream = stream;
+  // BLKQ4_GEMM_EARLY_WEIGHT_FETCH: programmatic stream serialization, see the kernel's entry
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (flags & BLKQ4_GEMM_EARLY_WEIGHT_FETCH) ? 1 : 0;
+  e = cudaLaunchKernelEx(&cfg, kern, tm_act, tm_pack, tm_scale, tm_zp, p);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return std::string(cudaGetErrorString(e));
   return std::string();
 }

@@ -120,8 +120,8 @@ int blkq4_fp16_quant_size_sm80(
  * kernel is then launched with programmatic stream serialization: it may become resident and
  * fetch weights while the preceding kernel of the stream still runs, which keeps HBM busy
  * across the launches of a decode stack.  Activations are read, and the output written, only
- * after the preceding work has completed, so stream order holds for both.  Honoured by the
- * skinny kernel (M <= 16); ignored elsewhere.
+ * after the preceding work has completed, so stream order holds for both (and for the split-K
+ * workspace).  Both the skinny and the tensor-core kernel honour it.
  */
 #define BLKQ4_GEMM_EARLY_WEIGHT_FETCH 1u
 int blkq4_fp16_gemm_sm100(

@@ -111,11 +111,13 @@ def test_streaming_skinny_kernel_shapes(case, flags):
     check_gaussian(block, True, has_zp, M, N, K, flags=flags)
 
 
-def test_early_weight_fetch_keeps_stream_order_for_activations():
+@pytest.mark.parametrize("M", [1, 64, 300])
+def test_early_weight_fetch_keeps_stream_order_for_activations(M):
     """A chain of layers on one stream, each consuming the previous output.  With
-    BLKQ4_GEMM_EARLY_WEIGHT_FETCH a launch may fetch weights while its predecessor still
-    runs, but must not read activations (or write its output) before the predecessor is
-    done: the chain's result must match the plainly serialized chain."""
+    BLKQ4_GEMM_EARLY_WEIGHT_FETCH a launch may fetch (and, in the tensor-core kernel, dequantize)
+    weights while its predecessor still runs, but must not read activations (or write its
+    output) before the predecessor is done: the chain's result must match the plainly
+    serialized chain.  M = 1: skinny kernel; 64 and 300: tensor-core kernel."""
     from gemmlib_b200 import capi
 
     K = N = 4096
@@ -123,13 +125,13 @@ def test_early_weight_fetch_keeps_stream_order_for_activations():
     for i in range(6):
         w = gaussian_weight(N, K, sigma=0.015, seed=100 + i)
         layers.append(tuple(to_cuda(x) for x in O.quant_prepack(64, True, w.numpy(), False)))
-    a0 = to_cuda(gaussian_act(1, K, seed=3).numpy())
+    a0 = to_cuda(gaussian_act(M, K, seed=3).numpy())
 
     def chain(flags):
-        bufs = [a0] + [torch.zeros(1, N, dtype=torch.float16, device="cuda") for _ in layers]
+        bufs = [a0] + [torch.zeros(M, N, dtype=torch.float16, device="cuda") for _ in layers]
         for _ in range(3):  # repeat: later rounds run with everything warm
             for i, (pw, ps, pz) in enumerate(layers):
-                capi.gemm(64, True, 1, N, K, bufs[i], pw, ps, pz, bufs[i + 1], flags=flags)
+                capi.gemm(64, True, M, N, K, bufs[i], pw, ps, pz, bufs[i + 1], flags=flags)
         torch.cuda.synchronize()
         assert capi.last_kernel_status() == 0
         return [b.float().cpu().numpy() for b in bufs[1:]]
@@ -137,8 +139,7 @@ def test_early_weight_fetch_keeps_stream_order_for_activations():
     plain, early = chain(0), chain(capi.EARLY_WEIGHT_FETCH)
     for i, (x, y) in enumerate(zip(plain, early)):
         assert np.isfinite(y).all()
-        # fp32 partial sums meet in shared memory in arrival order: equal up to fp16 rounding
-        assert np.abs(x - y).max() <= 2.0 ** -8 * max(1.0, np.abs(x).max()), i
+        assert (x == y).all(), i  # both kernels add their partial sums in a fixed order
 
 
 @pytest.mark.parametrize("case", [(64, True, False, 1, 2048, 1024), (64, True, True, 12, 352, 256),
