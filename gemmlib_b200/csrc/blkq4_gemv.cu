@@ -586,6 +586,7 @@ gemv_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_co
 #pragma unroll
       for (int u = 0; u < kUnitSteps; ++u) {
         const int step = sb * kUnitSteps + u;
+        if (step >= total_steps) break;  // the last unit of a K that is not a multiple of 512 (TMA zero-filled the rest)
         const uint4 wv = *reinterpret_cast<const uint4*>(wlane + u * 64);
         const int mr = (u >> bs) * 16;
         const float sa = __half2float(__ushort_as_half(sc[mr + g]));
@@ -691,7 +692,7 @@ std::string launch_persistent_T(int M, int N, int K, int block, cudaStream_t str
   if (gt) p.gt = *gt; p.M = M; p.N = N; p.K = K;
   p.block_shift = block == 64 ? 6 : 7;
   p.tiles = N / 16;
-  p.nsub = K / kUnitKBytes;
+  p.nsub = (K + kUnitKBytes - 1) / kUnitKBytes;  // the last unit may be partial
   p.ring = kRing;
   p.a_smem = (M <= 2 && (size_t)M * K * 2 <= 32 * 1024) ? 1 : 0;
   const int meta_rows = kUnitSteps >> (p.block_shift - 6);
@@ -777,9 +778,9 @@ std::string launch_gemv(int block, bool colwise, int M, int N, int K, cudaStream
   const int u = env_u ? env_u : 4;
   cudaError_t e;
   static const int env_generic = env_int("BLKQ4_GEMV_GENERIC");
-  // Fast path: one scale per 64-k step; K a multiple of 256 (whole units), meta rows and
-  // pointers 16-byte aligned (TMA), shared memory for the per-step terms within reach.
-  if (colwise && block >= 64 && !env_generic && K % kUnitKBytes == 0 && K <= 32768 &&
+  // Fast path: one scale per 64-k step; at least one 512-k unit (the last one may be partial), meta
+  // rows and pointers 16-byte aligned (TMA), shared memory for the per-step terms within reach.
+  if (colwise && block >= 64 && !env_generic && K >= kUnitKBytes && K <= 32768 &&
       reinterpret_cast<uintptr_t>(scales) % 16 == 0 && (!zp || reinterpret_cast<uintptr_t>(zp) % 16 == 0)) {
     const std::string r =
         (M <= 8) ? (zp ? launch_persistent_T<1, true>(M, N, K, block, stream, a, packed, scales, zp, out, bias, early)
@@ -809,7 +810,7 @@ std::string launch_gemv_gather(int block, bool colwise, int M, int N, int K, cud
                                const __half* a, const uint8_t* packed, const __half* scales,
                                const uint8_t* zp, const GatherTable& gt, unsigned flags) {
   if (M < 1 || M > 16) return "unsupported: the fused gather needs 1 <= M <= 16";
-  if (!(colwise && block >= 64 && K % kUnitKBytes == 0 && K <= 32768 &&
+  if (!(colwise && block >= 64 && K >= kUnitKBytes && K <= 32768 &&
         reinterpret_cast<uintptr_t>(scales) % 16 == 0 && (!zp || reinterpret_cast<uintptr_t>(zp) % 16 == 0)))
     return "unsupported: the fused gather runs on the column-wise block >= 64 fast path only";
   const bool early = (flags & BLKQ4_GEMM_EARLY_WEIGHT_FETCH) != 0;

@@ -81,7 +81,7 @@ class PeerGather:
     def supports(self, layer, rows: int) -> bool:
         """Shapes the fused kernel takes (the library refuses the others)."""
         return (rows <= min(16, self.max_rows) and layer.col_wise and layer.block_size >= 64
-                and layer.in_features % 512 == 0 and layer.in_features <= 32768
+                and 512 <= layer.in_features <= 32768
                 and layer.out_features * self.world == self.out_features)
 
     def forward(self, layer, x, out_full, flags=0):

@@ -198,7 +198,7 @@ int blkq4_fp16_gemm_static_ws_sm100(
  * buffers over NVLink and raises a per-rank flag; a second small kernel waits (bounded, ~1 s)
  * for all flags and copies the gathered rows out.  All ranks must make the same sequence of
  * calls; work that reads output_ptr must be enqueued on `stream` before the next gather call.
- * A shape outside the skinny kernel's TMA fast path (column-wise, block >= 64, K % 512 == 0,
+ * A shape outside the skinny kernel's TMA fast path (column-wise, block >= 64, 512 <= K <= 32768,
  * M <= 16) is refused with an error text starting "Kernel execution failed: unsupported":
  * compute with blkq4_fp16_gemm_sm80 and all-gather with the caller's collective instead.
  * blkq4_gather_status synchronises `stream` and returns 0, or (0x400 | rank) of the first

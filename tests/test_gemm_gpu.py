@@ -101,6 +101,7 @@ STREAM_CASES = [
     (64, False, 1, 4736, 1024), (64, True, 3, 2400, 1280), (128, False, 8, 160, 3072),
     (128, True, 16, 4768, 2048), (64, True, 9, 2432, 5120), (64, False, 2, 1600, 16384),
     (128, True, 16, 64, 32768),  # per-step terms would not fit in shared memory: generic kernel
+    (64, True, 1, 4096, 11008), (128, False, 5, 512, 1664),  # K not a multiple of 512: partial last unit
 ]
 
 
