@@ -697,7 +697,8 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
   const int grid = p.num_items < sms ? p.num_items : sms;
   const SmemPlan plan = make_plan(p.BM);
   auto kern = colwise ? gemm_tc_kernel<true> : gemm_tc_kernel<false>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.total);
+  static std::atomic<int> granted[2][64];
+  cudaError_t e = ensure_dynamic_smem(kern, plan.total, granted[colwise ? 1 : 0]);
   if (e != cudaSuccess) return std::string(cudaGetErrorString(e));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);

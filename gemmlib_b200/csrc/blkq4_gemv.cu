@@ -720,7 +720,8 @@ std::string launch_persistent_T(int M, int N, int K, int block, cudaStream_t str
                       (p.a_smem ? (size_t)M * K * 2 : 0);
   if (smem > kMaxDynamicSmem) return kTooMuchSmem;  // very long K with 9..16 rows: the generic kernel takes it
   auto kern = gemv_persistent_kernel<MT, HAS_ZP>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  static std::atomic<int> granted[64];
+  cudaError_t e = ensure_dynamic_smem(kern, smem, granted);
   if (e != cudaSuccess) return std::string(cudaGetErrorString(e));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);

@@ -7,6 +7,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+#include <memory>
+
 namespace blkq4 {
 
 using TensorMapEncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -29,17 +32,45 @@ inline TensorMapEncodeFn tensor_map_encode_fn() {
 // 2-D row-major tensor [rows][cols] of `elt` bytes per element; box = box_rows x box_cols.
 // Requirements (checked by the driver): 16-byte aligned base, row pitch a multiple of 16
 // bytes, box_cols * elt a multiple of 16 bytes, box extents <= 256.
+// A descriptor is a pure function of the arguments below, and a decode loop asks for the same few
+// hundred descriptors over and over: a small per-thread direct-mapped cache takes the driver call
+// (~1 us each, three or four per launch) off the launch path.
 inline bool encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int elt, const void* ptr,
                                  uint64_t cols, uint64_t rows, uint32_t box_cols, uint32_t box_rows,
                                  CUtensorMapSwizzle swz) {
+  struct Entry {
+    const void* ptr;
+    uint64_t cols, rows;
+    uint32_t box_cols, box_rows;
+    int dt, elt, swz;
+    bool valid;
+    CUtensorMap map;
+  };
+  constexpr int kEntries = 1024;
+  thread_local std::unique_ptr<Entry[]> cache_mem;
+  if (!cache_mem) cache_mem.reset(new Entry[kEntries]());
+  Entry* cache = cache_mem.get();
+  uint64_t h = reinterpret_cast<uintptr_t>(ptr) >> 4;
+  h ^= (cols * 0x9e3779b97f4a7c15ull) ^ (rows * 0xc2b2ae3d27d4eb4full) ^ ((uint64_t)box_cols << 20) ^
+       ((uint64_t)box_rows << 8) ^ (uint64_t)swz ^ ((uint64_t)dt << 4);
+  h ^= h >> 29;
+  Entry& e = cache[h % kEntries];
+  if (e.valid && e.ptr == ptr && e.cols == cols && e.rows == rows && e.box_cols == box_cols &&
+      e.box_rows == box_rows && e.dt == (int)dt && e.elt == elt && e.swz == (int)swz) {
+    *map = e.map;
+    return true;
+  }
   TensorMapEncodeFn fn = tensor_map_encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {cols * (uint64_t)elt};
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  return fn(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  if (fn(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  e = Entry{ptr, cols, rows, box_cols, box_rows, (int)dt, elt, (int)swz, true, *map};
+  return true;
 }
 
 // 3-D tensor of `elt`-byte elements with explicit byte strides for dimensions 1 and 2 (dimension 0
@@ -56,6 +87,19 @@ inline bool encode_tensor_map_3d(CUtensorMap* map, CUtensorMapDataType dt, const
   cuuint32_t estr[3] = {1, 1, 1};
   return fn(map, dt, 3, const_cast<void*>(ptr), d, st, b, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize is per device and sticky: raise it only when a launch
+// needs more than an earlier one asked for.  `granted` is one table per kernel instance.
+template <typename Kernel>
+inline cudaError_t ensure_dynamic_smem(Kernel kern, size_t bytes, std::atomic<int> (&granted)[64]) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev >= 0 && dev < 64 && granted[dev].load(std::memory_order_relaxed) >= (int)bytes) return cudaSuccess;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e == cudaSuccess && dev >= 0 && dev < 64) granted[dev].store((int)bytes, std::memory_order_relaxed);
+  return e;
 }
 
 #ifdef __CUDACC__
