@@ -74,9 +74,23 @@ class PeerGather:
             dist.all_gather_object(handles, self.ctx.handle, group=group)
         else:
             handles[0] = self.ctx.handle
-        self.ctx.connect(handles)
+        error = None
+        try:
+            self.ctx.connect(handles)
+        except Exception as exc:  # noqa: BLE001  (reported on every rank below)
+            error = exc
         if self.world > 1:
-            dist.barrier(group=group)  # nobody stores into a block before everybody has mapped it
+            # Doubles as the barrier "nobody stores into a block before everybody has mapped it";
+            # a rank that could not map its peers must not leave the others waiting in a collective.
+            flags = [None] * self.world
+            dist.all_gather_object(flags, error is None, group=group)
+            if not all(flags):
+                self.ctx.close()
+                raise RuntimeError("PeerGather: mapping the peers' exchange blocks failed on rank(s) "
+                                   + ", ".join(str(r) for r, ok in enumerate(flags) if not ok)
+                                   + (f" (here: {error})" if error is not None else ""))
+        elif error is not None:
+            raise error
 
     def supports(self, layer, rows: int) -> bool:
         """Shapes the fused kernel takes (the library refuses the others)."""
