@@ -73,22 +73,6 @@ inline bool encode_tensor_map_2d(CUtensorMap* map, CUtensorMapDataType dt, int e
   return true;
 }
 
-// 3-D tensor of `elt`-byte elements with explicit byte strides for dimensions 1 and 2 (dimension 0
-// is contiguous).  The strides need not grow with the dimension index: a box is written to shared
-// memory in dimension order, so listing a small-stride dimension last transposes on the fly.
-inline bool encode_tensor_map_3d(CUtensorMap* map, CUtensorMapDataType dt, const void* ptr,
-                                 const uint64_t dims[3], const uint64_t strides_bytes[2],
-                                 const uint32_t box[3], CUtensorMapSwizzle swz) {
-  TensorMapEncodeFn fn = tensor_map_encode_fn();
-  if (!fn) return false;
-  cuuint64_t d[3] = {dims[0], dims[1], dims[2]};
-  cuuint64_t st[2] = {strides_bytes[0], strides_bytes[1]};
-  cuuint32_t b[3] = {box[0], box[1], box[2]};
-  cuuint32_t estr[3] = {1, 1, 1};
-  return fn(map, dt, 3, const_cast<void*>(ptr), d, st, b, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
-            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 // cudaFuncAttributeMaxDynamicSharedMemorySize is per device and sticky: raise it only when a launch
 // needs more than an earlier one asked for.  `granted` is one table per kernel instance.
 template <typename Kernel>
@@ -130,35 +114,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// try_wait with a suspend-time hint: the hardware parks the thread for up to `ns` nanoseconds or
-// until the phase completes, so a waiting warp does not compete for issue slots.
-__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t ns) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(ns)
-      : "memory");
-  return ok != 0;
-}
-// mbar_wait_bounded for waits that are usually long (a consumer waiting for HBM): same contract,
-// but the thread is parked in hardware between polls.
-__device__ __forceinline__ bool mbar_wait_bounded_parked(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                                         int* error_word, int who, long long max_cycles) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  for (;;) {
-    if (mbar_try_wait_suspend(bar, parity, 20000u)) return true;
-    if (*abort_flag) return false;
-    if (clock64() - t0 > max_cycles) {
-      *abort_flag = 1;
-      atomicCAS(error_word, 0, who);
-      return false;
-    }
-  }
-}
 // Bounded wait: gives up after `max_cycles`, or as soon as another thread of the CTA has
 // given up (abort_flag, in shared memory).  On expiry records `who` in *error_word (global)
 // and returns false; the caller drains instead of hanging the GPU.
@@ -181,13 +136,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z,
-                                            uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
       : "memory");
 }
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
