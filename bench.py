@@ -574,6 +574,54 @@ def bench_reference_gpu(torch, dev, layers_c2, a_dev):
     us = e0.elapsed_time(e1) * 1e3 / (reps * sets)
     out["c3_gemm"] = {"us_per_call": round(us, 2), "TFLOP/s": round(2.0 * c["M"] * c["N"] * c["K"] / us / 1e6, 1),
                       "timing": "plain launches"}
+    # ---- configs[0]: M=16 K=N=4096 block 32 zero points (the reference's small-M tile), both libraries,
+    #      16 weight sets (16 x 10 MB > L2), CUDA-graph replay where the launcher can be captured ----
+    c1 = dict(M=16, K=4096, N=4096, block=32)
+    g = torch.Generator().manual_seed(300)
+    lyrs1 = [BlkQ4Linear(c1["block"], True, False, (torch.randn(c1["N"], c1["K"], generator=g) * 0.02).half().to(dev))
+             for _ in range(16)]
+    x1 = torch.randn(c1["M"], c1["K"], generator=g).half().to(dev)
+    o1 = torch.empty(c1["M"], c1["N"], dtype=torch.float16, device=dev)
+    o1_ref = torch.empty_like(o1)
+
+    def ref_pass(st):
+        for lyr in lyrs1:
+            call(c1["block"], True, c1["M"], c1["N"], c1["K"], st, x1, lyr.q_weights, lyr.q_scales, lyr.q_zp, o1_ref)
+
+    def our_pass(st):
+        for lyr in lyrs1:
+            lyr(x1, out=o1)
+
+    def timed(pass_fn):
+        with torch.cuda.stream(stream):
+            for _ in range(2):
+                pass_fn(stream.cuda_stream)
+        torch.cuda.synchronize()
+        try:
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=stream):
+                pass_fn(stream.cuda_stream)
+            run_, how_ = gr.replay, "CUDA-graph replay"
+        except Exception:
+            torch.cuda.synchronize()
+            run_, how_ = (lambda: pass_fn(0)), "plain launches"
+        for _ in range(3):
+            run_()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(50):
+            run_()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / (50 * len(lyrs1)), how_
+
+    nbytes1 = algorithmic_bytes(c1["M"], c1["K"], c1["N"], c1["block"], True, True)
+    us_ref, how_ref = timed(ref_pass)
+    us_our, how_our = timed(our_pass)
+    out["c1_max_abs_diff_vs_ours"] = float((o1_ref.float() - o1.float()).abs().max())
+    out["c1_m16"] = {"reference_us": round(us_ref, 2), "reference_GB/s": round(nbytes1 / us_ref / 1e3, 1),
+                     "ours_us": round(us_our, 2), "ours_GB/s": round(nbytes1 / us_our / 1e3, 1),
+                     "timing": how_ref if how_ref == how_our else how_ref + " / " + how_our}
     out["what"] = "reference CUDA kernels (mma.sync path) compiled for sm_100a, same packed tensors, same GPU"
     return out
 
