@@ -29,6 +29,16 @@ std::string launch_gemv(int block, bool colwise, int M, int N, int K, cudaStream
                         const __half* a, const uint8_t* packed, const __half* scales,
                         const uint8_t* zp, __half* out, const __half* bias, unsigned flags);
 
+// The decode kernel (M <= 8, column-wise blocks >= 64, K a multiple of 256 and >= 2048): per-warp
+// cp.async rings, two launches resident per SM.  Returns kStreamUnsupported for other shapes.
+extern const char* const kStreamUnsupported;
+std::string launch_gemv_stream(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
+                               const __half* a, const uint8_t* packed, const __half* scales,
+                               const uint8_t* zp, __half* out, const __half* bias, unsigned flags);
+
+// Multiprocessor count of the CURRENT device (cached per device index).
+int sm_count();
+
 // ---- fused GEMV + all-gather over peer memory (one process per GPU, one box) ----------------
 // Every rank owns one device block, mapped by all peers (CUDA IPC):
 //   [0]   uint32 epoch      layer calls completed by this rank

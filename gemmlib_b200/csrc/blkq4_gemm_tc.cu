@@ -591,16 +591,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
 
 namespace {
 
-int sm_count() {
-  static int sms = 0;
-  if (!sms) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  }
-  return sms;
-}
-
 // Split-K plan.  The kernel is persistent with one CTA per SM, so a problem with few output
 // tiles (prefill of a 4096-wide layer at M = 512: 64 tiles on 148 SMs) leaves SMs idle; cutting
 // every tile's K range in `split` work items fills them.

@@ -707,12 +707,7 @@ std::string launch_persistent_T(int M, int N, int K, int block, cudaStream_t str
                                   (uint64_t)(K / block), 16, (uint32_t)meta_rows, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (!ok) return "cuTensorMapEncodeTiled failed";
 
-  static int sms = 0;
-  if (!sms) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  }
+  const int sms = sm_count();
   const int grid = p.tiles < sms ? p.tiles : sms;
   const size_t smem = kCtrlBytes + (size_t)kRing * kSlotBytes +
                       (size_t)(MT == 1 ? kAccBufsMax : 2) * kCons * MT * 4 * 32 * sizeof(float) +
@@ -759,6 +754,20 @@ cudaError_t launch_T(int warps, int M, int N, int K, int block, cudaStream_t str
 
 }  // namespace
 
+int sm_count() {
+  static std::atomic<int> cache[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (dev >= 0 && dev < 64) {
+    const int c = cache[dev].load(std::memory_order_relaxed);
+    if (c > 0) return c;
+  }
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return 148;
+  if (dev >= 0 && dev < 64) cache[dev].store(sms, std::memory_order_relaxed);
+  return sms;
+}
+
 int read_gemv_error() {
   int v = 0;
   if (cudaMemcpyFromSymbol(&v, g_gemv_error, sizeof(int)) != cudaSuccess) return -1;
@@ -778,7 +787,12 @@ std::string launch_gemv(int block, bool colwise, int M, int N, int K, cudaStream
   if (env_warps >= 1 && env_warps <= kMaxWarps) warps = env_warps;
   const int u = env_u ? env_u : 4;
   cudaError_t e;
-  static const int env_generic = env_int("BLKQ4_GEMV_GENERIC");
+  static const int env_generic = env_int("BLKQ4_GEMV_GENERIC"), env_no_stream = env_int("BLKQ4_GEMV_NO_STREAM");
+  // Decode shapes first: the cp.async stream kernel (blkq4_gemv_stream.cu).
+  if (!env_generic && !env_no_stream) {
+    const std::string r = launch_gemv_stream(block, colwise, M, N, K, stream, a, packed, scales, zp, out, bias, flags);
+    if (r != kStreamUnsupported) return r;
+  }
   // Fast path: one scale per 64-k step; at least one 512-k unit (the last one may be partial), meta
   // rows and pointers 16-byte aligned (TMA), shared memory for the per-step terms within reach.
   if (colwise && block >= 64 && !env_generic && K >= kUnitKBytes && K <= 32768 &&
