@@ -32,9 +32,11 @@ std::string launch_gemv(int block, bool colwise, int M, int N, int K, cudaStream
 // The decode kernel (M <= 8, column-wise blocks >= 64, K a multiple of 256 and >= 2048): per-warp
 // cp.async rings, two launches resident per SM.  Returns kStreamUnsupported for other shapes.
 extern const char* const kStreamUnsupported;
+struct GatherTable;
 std::string launch_gemv_stream(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
                                const __half* a, const uint8_t* packed, const __half* scales,
-                               const uint8_t* zp, __half* out, const __half* bias, unsigned flags);
+                               const uint8_t* zp, __half* out, const __half* bias, unsigned flags,
+                               const GatherTable* gt = nullptr);
 
 // Multiprocessor count of the CURRENT device (cached per device index).
 int sm_count();
@@ -45,11 +47,13 @@ int sm_count();
 //   [4]   uint32 done_ctr   CTAs of the running call that have finished storing
 //   [8]   int    error      first wait that expired (0 = none)
 //   [12]  uint32 tickets    CTAs of the wait kernel started so far (kGatherWaitCtas per call)
-//   [64]  uint32 flags[2][kGatherMaxRanks]   flags[slot][src] = epoch whose slice from `src` landed
+//   [64]  uint32 flags[2][kGatherMaxRanks]   flags[slot][src] = epoch whose slice from `src` landed (two-kernel protocol)
+//   [128] uint32 arrivals[2][kGatherMaxRanks] CTAs of `src` that have delivered their tiles (one-kernel protocol)
 //   [kGatherCtrlBytes]  gathered[2][buf_bytes]  the [M, N_total] results of even / odd epochs
 constexpr int kGatherMaxRanks = 8;
 constexpr int kGatherCtrlBytes = 1024;
-constexpr int kGatherEpochOff = 0, kGatherDoneOff = 4, kGatherErrorOff = 8, kGatherTicketOff = 12, kGatherFlagsOff = 64;
+constexpr int kGatherEpochOff = 0, kGatherDoneOff = 4, kGatherErrorOff = 8, kGatherTicketOff = 12, kGatherFlagsOff = 64,
+              kGatherArrivalsOff = 128;
 constexpr int kGatherWaitCtas = 8;  // fixed grid of the wait kernel: its call number is tickets / 8
 
 struct GatherTable {
@@ -60,10 +64,13 @@ struct GatherTable {
 };
 
 // The skinny kernel with its epilogue storing this rank's [M, N] slice straight into every
-// rank's gathered buffer.  Returns "unsupported" when the shape is not on the TMA fast path.
+// rank's gathered buffer.  *delivered = true: the launch also waited for the peers and copied the
+// complete result to out_full (decode kernel); false: the caller launches the wait-and-copy kernel.
+// Returns "unsupported" when the shape is on neither fast path.
 std::string launch_gemv_gather(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
                                const __half* a, const uint8_t* packed, const __half* scales,
-                               const uint8_t* zp, const GatherTable& gt, unsigned flags);
+                               const uint8_t* zp, __half* out_full, const GatherTable& gt, unsigned flags,
+                               bool* delivered);
 
 std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
                            const __half* a, const uint8_t* packed, const __half* scales,

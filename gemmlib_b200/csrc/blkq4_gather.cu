@@ -191,11 +191,14 @@ extern "C" int blkq4_fp16_gemm_gather_sm100(void* ctx, int block_size, bool colu
   gt.n_total = (int)n_total;
   gt.buf_bytes = c->buf_bytes;
   auto stream = reinterpret_cast<cudaStream_t>(stream_ptr);
+  bool delivered = false;
   const std::string e = blkq4::launch_gemv_gather(
       block_size, column_wise_blocking, m, n_shard, k, stream, reinterpret_cast<const __half*>(act_ptr),
       reinterpret_cast<const uint8_t*>(weights_ptr), reinterpret_cast<const __half*>(scales_ptr),
-      has_offsets ? reinterpret_cast<const uint8_t*>(offsets_ptr) : nullptr, gt, flags);
+      has_offsets ? reinterpret_cast<const uint8_t*>(offsets_ptr) : nullptr, reinterpret_cast<__half*>(output_ptr),
+      gt, flags, &delivered);
   if (!e.empty()) return blkq4::fail(err, "Kernel execution failed: " + e);
+  if (delivered) return 0;  // one launch did everything
   const unsigned long long n16 = output_size / 16;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(blkq4::kGatherWaitCtas);

@@ -823,8 +823,20 @@ std::string launch_gemv(int block, bool colwise, int M, int N, int K, cudaStream
 
 std::string launch_gemv_gather(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
                                const __half* a, const uint8_t* packed, const __half* scales,
-                               const uint8_t* zp, const GatherTable& gt, unsigned flags) {
+                               const uint8_t* zp, __half* out_full, const GatherTable& gt, unsigned flags,
+                               bool* delivered) {
+  *delivered = false;
   if (M < 1 || M > 16) return "unsupported: the fused gather needs 1 <= M <= 16";
+  // Decode shapes: the stream kernel computes, exchanges, waits and copies out in one launch.
+  static const int env_no_stream = env_int("BLKQ4_GEMV_NO_STREAM");
+  if (!env_no_stream) {
+    const std::string r = launch_gemv_stream(block, colwise, M, N, K, stream, a, packed, scales, zp, out_full, nullptr,
+                                             flags, &gt);
+    if (r != kStreamUnsupported) {
+      *delivered = r.empty();
+      return r;
+    }
+  }
   if (!(colwise && block >= 64 && K >= kUnitKBytes && K <= 32768 &&
         reinterpret_cast<uintptr_t>(scales) % 16 == 0 && (!zp || reinterpret_cast<uintptr_t>(zp) % 16 == 0)))
     return "unsupported: the fused gather runs on the column-wise block >= 64 fast path only";

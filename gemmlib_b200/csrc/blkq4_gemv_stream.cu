@@ -62,7 +62,19 @@ struct StreamParams {
   int tiles;        // N / 16
   int steps;        // K / 64
   int a_pitch;      // halves per activation row in shared memory (K + 8: rows land on different banks)
+  GatherTable gt;   // gather mode: the result goes to every rank's gathered buffer, then to `out` as [M, world * N]
 };
+
+constexpr long long kGatherWaitCycles = 2000000000ll;  // ~1 s
+
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add(unsigned* p, unsigned v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 
 __device__ __forceinline__ uint32_t lop3_and_or(uint32_t x, uint32_t mask, uint32_t bits) {
   uint32_t d;
@@ -132,9 +144,18 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // Shared memory: rings [kWarps][D][kSlotBytes] | s_corr [steps][4] float4 | s_asum [steps][8] (zero points)
-//                | s_part [2][PW][16][MS] | s_a [M][a_pitch]
+//                | s_part [2][PW][16][MS] | s_stage [8][16] fp16 (gather) | s_a [M][a_pitch]
 // MZ: rows of the zero-point accumulators kept in registers (2 for M <= 2, else 8).
-template <bool HAS_ZP, int D, int MZ>
+//
+// GATHER (N-sharded layer, one process per GPU): the adding warp stores the tile's fp16 results into
+// EVERY rank's gathered buffer with 16-byte peer stores; when a CTA has stored its last tile it adds
+// one to this rank's arrival counter in every rank's block (red.release.sys); then every CTA waits -
+// bounded - until the counters of all ranks have reached the grid size, copies its share of the
+// complete [M, world * N] result to `out`, and the last CTA re-arms the counters and advances the
+// epoch.  One launch per layer; nothing polls from a second kernel.  Epochs alternate between two
+// buffers and two counter sets: a peer reaches epoch e + 2 only after this rank's arrivals of epoch
+// e + 1, which follow (stream order) the completion of this rank's launch of epoch e.
+template <bool HAS_ZP, int D, int MZ, bool GATHER>
 __global__ void __launch_bounds__(kWarps * 32, 2)
 gemv_stream_kernel(const StreamParams p) {
   extern __shared__ __align__(16) uint8_t s_raw[];
@@ -145,7 +166,8 @@ gemv_stream_kernel(const StreamParams p) {
   float* s_corr = reinterpret_cast<float*>(s_ring + W * D * kSlotBytes);
   float* s_asum = s_corr + (size_t)p.steps * 16;
   float* s_part = s_asum + (HAS_ZP ? (size_t)p.steps * 8 : 0);
-  __half* s_a = reinterpret_cast<__half*>(s_part + (size_t)2 * PW * 16 * MS);
+  __half* s_stage = reinterpret_cast<__half*>(s_part + (size_t)2 * PW * 16 * MS);
+  __half* s_a = s_stage + 128;
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
@@ -215,6 +237,15 @@ gemv_stream_kernel(const StreamParams p) {
 
   // Activations and the output belong to stream order.
   asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  // Gather mode: this call's epoch is one past the calls this rank has completed (the word changes
+  // only at the very end of a launch, and the preceding launch has completed: see the wait above).
+  unsigned gather_epoch = 0;
+  size_t gather_off = 0;
+  if (GATHER) {
+    gather_epoch = *reinterpret_cast<volatile unsigned*>(p.gt.base[p.gt.rank] + kGatherEpochOff) + 1u;
+    gather_off = kGatherCtrlBytes + (size_t)(gather_epoch & 1u) * p.gt.buf_bytes;
+  }
 
   // ---- per warp: its own K slice of the activations into shared memory, and the activation-only
   //      terms of its steps.  Chunk c = 8 halves; even c is the "lo" half (k % 16 < 8) of a 16-k block.
@@ -361,16 +392,74 @@ gemv_stream_kernel(const StreamParams p) {
         const int n = tile * 16 + row;
         // bias joins the ROUNDED result in fp16, as a separate `output += bias` would
         const __half h = __float2half_rn(sum);
-        p.out[(size_t)m * N + n] = p.bias ? __hadd(h, p.bias[n]) : h;
+        if (GATHER) s_stage[idx] = h;  // [m][16]
+        else p.out[(size_t)m * N + n] = p.bias ? __hadd(h, p.bias[n]) : h;
+      }
+      if (GATHER) {
+        // this rank's 16 columns of row m, as two 16-byte pieces, into every rank's gathered buffer
+        __syncwarp();
+        if (lane < 2 * M) {
+          const int m = lane >> 1, piece = lane & 1;
+          const uint4 v = *reinterpret_cast<const uint4*>(s_stage + m * 16 + piece * 8);
+          const size_t off = gather_off +
+              ((size_t)m * p.gt.n_total + (size_t)p.gt.rank * N + (size_t)tile * 16 + piece * 8) * sizeof(__half);
+          for (int r = 0; r < p.gt.world; ++r) *reinterpret_cast<uint4*>(p.gt.base[r] + off) = v;
+        }
+        __syncwarp();
       }
     }
   }
   cp_async_wait<0>();
+  if (GATHER) {
+    uint8_t* local = p.gt.base[p.gt.rank];
+    const unsigned slot = gather_epoch & 1u;
+    // every adding warp's peer stores are ordered before the barrier; one thread publishes them
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      const size_t aoff = kGatherArrivalsOff + ((size_t)slot * kGatherMaxRanks + p.gt.rank) * sizeof(unsigned);
+      for (int r = 0; r < p.gt.world; ++r) red_release_sys_add(reinterpret_cast<unsigned*>(p.gt.base[r] + aoff), 1u);
+    }
+    // wait, bounded, for every rank's CTAs (all ranks launch the same grid)
+    if ((int)threadIdx.x < p.gt.world) {
+      const unsigned* ctr = reinterpret_cast<const unsigned*>(local + kGatherArrivalsOff) + slot * kGatherMaxRanks + threadIdx.x;
+      const long long t0 = clock64();
+      while (ld_acquire_sys(ctr) < gridDim.x) {
+        if (clock64() - t0 > kGatherWaitCycles) {
+          atomicCAS(reinterpret_cast<int*>(local + kGatherErrorOff), 0, 0x400 | (int)threadIdx.x);
+          break;
+        }
+      }
+    }
+    __syncthreads();
+    // copy this CTA's share of the complete result out (peers wrote it over NVLink: read around L1)
+    const unsigned long long n16 = (unsigned long long)M * p.gt.n_total * sizeof(__half) / 16;
+    const uint4* src = reinterpret_cast<const uint4*>(local + gather_off);
+    uint4* dst = reinterpret_cast<uint4*>(p.out);
+    for (unsigned long long i = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; i < n16;
+         i += (unsigned long long)gridDim.x * blockDim.x)
+      dst[i] = __ldcg(src + i);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      const unsigned arrived = atomicAdd(reinterpret_cast<unsigned*>(local + kGatherDoneOff), 1u);
+      if (arrived == gridDim.x - 1) {
+        // last CTA of this rank: re-arm this slot's counters, keep the two-kernel protocol's ticket
+        // numbering in step (its wait kernel draws kGatherWaitCtas tickets per call), advance the epoch
+        unsigned* ctrs = reinterpret_cast<unsigned*>(local + kGatherArrivalsOff) + slot * kGatherMaxRanks;
+        for (int r = 0; r < kGatherMaxRanks; ++r) ctrs[r] = 0u;
+        *reinterpret_cast<volatile unsigned*>(local + kGatherDoneOff) = 0u;
+        atomicAdd(reinterpret_cast<unsigned*>(local + kGatherTicketOff), (unsigned)kGatherWaitCtas);
+        __threadfence();
+        *reinterpret_cast<volatile unsigned*>(local + kGatherEpochOff) = gather_epoch;
+      }
+    }
+  }
 }
 
-template <bool HAS_ZP, int D, int MZ>
+template <bool HAS_ZP, int D, int MZ, bool GATHER>
 std::string launch_T(const StreamParams& p, size_t smem, int grid, cudaStream_t stream, bool early) {
-  auto kern = gemv_stream_kernel<HAS_ZP, D, MZ>;
+  auto kern = gemv_stream_kernel<HAS_ZP, D, MZ, GATHER>;
   static std::atomic<int> granted[64];
   cudaError_t e = ensure_dynamic_smem(kern, smem, granted);
   if (e != cudaSuccess) return std::string(cudaGetErrorString(e));
@@ -393,7 +482,7 @@ std::string launch_T(const StreamParams& p, size_t smem, int grid, cudaStream_t 
 size_t stream_smem_bytes(int M, int K, bool has_zp, int D) {
   const int MS = (M + 1) & ~1, PW = has_zp ? 2 * kWarps : kWarps, steps = K / 64;
   return (size_t)kWarps * D * kSlotBytes + (size_t)steps * 64 + (has_zp ? (size_t)steps * 32 : 0) +
-         (size_t)2 * PW * 16 * MS * 4 + (size_t)M * (K + 8) * 2;
+         (size_t)2 * PW * 16 * MS * 4 + 256 + (size_t)M * (K + 8) * 2;
 }
 
 }  // namespace
@@ -403,7 +492,8 @@ const char* const kStreamUnsupported = "unsupported by the stream kernel";
 // Returns kStreamUnsupported when the shape is outside this kernel (the caller then takes another one).
 std::string launch_gemv_stream(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
                                const __half* a, const uint8_t* packed, const __half* scales,
-                               const uint8_t* zp, __half* out, const __half* bias, unsigned flags) {
+                               const uint8_t* zp, __half* out, const __half* bias, unsigned flags,
+                               const GatherTable* gt) {
   const int group_k = kGroupSteps * 64;
   if (!colwise || block < 64 || M < 1 || M > 8 || K % group_k != 0 || K / group_k < kWarps ||
       reinterpret_cast<uintptr_t>(scales) % 16 != 0 || (zp && reinterpret_cast<uintptr_t>(zp) % 16 != 0) ||
@@ -428,24 +518,29 @@ std::string launch_gemv_stream(int block, bool colwise, int M, int N, int K, cud
   p.tiles = N / 16;
   p.steps = K / 64;
   p.a_pitch = K + 8;
+  if (gt) p.gt = *gt;
   const int sms = sm_count();
   // One CTA per SM leaves the second CTA slot of every SM to the next launch (its weights stream in
   // while this launch computes).  Two per SM double the warps that compute; worth it only when the
   // tiles then still divide evenly enough.
   int grid = p.tiles < sms ? p.tiles : sms;
-  if (smem <= kHalfSm && p.tiles > sms) {
+  if (!gt && smem <= kHalfSm && p.tiles > sms) {  // gather mode: one CTA per SM, so that the whole grid is resident while it waits
     const int per2 = (p.tiles + 2 * sms - 1) / (2 * sms);
     const double eff2 = (double)p.tiles / (2.0 * sms) / per2;
     if (eff2 >= 0.85) grid = p.tiles < 2 * sms ? p.tiles : 2 * sms;
   }
   const bool early = (flags & BLKQ4_GEMM_EARLY_WEIGHT_FETCH) != 0;
   const bool small_m = M <= 2;
-  if (zp) {
-    if (D == 4) return small_m ? launch_T<true, 4, 2>(p, smem, grid, stream, early) : launch_T<true, 4, 8>(p, smem, grid, stream, early);
-    return small_m ? launch_T<true, 2, 2>(p, smem, grid, stream, early) : launch_T<true, 2, 8>(p, smem, grid, stream, early);
-  }
-  if (D == 4) return launch_T<false, 4, 2>(p, smem, grid, stream, early);
-  return launch_T<false, 2, 2>(p, smem, grid, stream, early);
+#define BLKQ4_STREAM_LAUNCH(G)                                                                                     \
+  if (zp) {                                                                                                          \
+    if (D == 4) return small_m ? launch_T<true, 4, 2, G>(p, smem, grid, stream, early) : launch_T<true, 4, 8, G>(p, smem, grid, stream, early); \
+    return small_m ? launch_T<true, 2, 2, G>(p, smem, grid, stream, early) : launch_T<true, 2, 8, G>(p, smem, grid, stream, early); \
+  }                                                                                                                  \
+  if (D == 4) return launch_T<false, 4, 2, G>(p, smem, grid, stream, early);                                         \
+  return launch_T<false, 2, 2, G>(p, smem, grid, stream, early);
+  if (gt) { BLKQ4_STREAM_LAUNCH(true) }
+  BLKQ4_STREAM_LAUNCH(false)
+#undef BLKQ4_STREAM_LAUNCH
 }
 
 }  // namespace blkq4

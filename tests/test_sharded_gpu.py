@@ -66,14 +66,15 @@ def test_unsupported_shape_is_refused_not_miscomputed():
     pg.close()
 
 
-def test_missing_peer_expires_the_bounded_wait_and_reports_it():
+@pytest.mark.parametrize("K", [1024, 2048])  # two-kernel protocol (TMA skinny kernel) / one-kernel (decode kernel)
+def test_missing_peer_expires_the_bounded_wait_and_reports_it(K):
     """Failure detection without a GPU fault: rank 0 of a two-rank exchange runs, rank 1 never
-    does (its flag is a word nothing sets).  The wait kernel gives up after its ~1 s limit,
-    records (0x400 | rank 1), and the context, the stream and the device stay usable."""
+    does (its flag / arrival counter is a word nothing sets).  The wait gives up after its ~1 s
+    limit, records (0x400 | rank 1), and the context, the stream and the device stay usable."""
     from gemmlib_b200 import capi
     from gemmlib_b200.ms_blkq4linear import BlkQ4Linear
 
-    K, ns = 1024, 256
+    ns = 256
     layer = BlkQ4Linear(64, True, True, gaussian_weight(ns, K, seed=2).cuda())
     x = gaussian_act(1, K, seed=3).cuda()
     a = capi.GatherContext(2, 0, 16 * 2 * ns * 2)
@@ -89,6 +90,11 @@ def test_missing_peer_expires_the_bounded_wait_and_reports_it():
     torch.cuda.synchronize()
     assert torch.allclose(out[:, :ns].float(), want.float(), atol=2.0 ** -8 * max(1.0, float(want.abs().max())), rtol=0)
     assert capi.last_kernel_status() == 0
+    # the context keeps working: the next call of the same (still lonely) rank expires the same way
+    out.zero_()
+    a.gemm(64, True, 1, ns, K, x, layer.q_weights, layer.q_scales, None, out)
+    assert a.status() == (0x400 | 1)
+    assert torch.allclose(out[:, :ns].float(), want.float(), atol=2.0 ** -8 * max(1.0, float(want.abs().max())), rtol=0)
     a.close()
     b.close()
 
