@@ -48,12 +48,11 @@ int sm_count();
 //   [8]   int    error      first wait that expired (0 = none)
 //   [12]  uint32 tickets    CTAs of the wait kernel started so far (kGatherWaitCtas per call)
 //   [64]  uint32 flags[2][kGatherMaxRanks]   flags[slot][src] = epoch whose slice from `src` landed (two-kernel protocol)
-//   [128] uint32 arrivals[2][kGatherMaxRanks] CTAs of `src` that have delivered their tiles (one-kernel protocol)
-//   [kGatherCtrlBytes]  gathered[2][buf_bytes]  the [M, N_total] results of even / odd epochs
+//   [kGatherCtrlBytes]                  gathered[2][buf_bytes]     fp16 [M, N_total] of even / odd epochs (two-kernel protocol)
+//   [kGatherCtrlBytes + 2 buf_bytes]    flagged[2][2 * buf_bytes]  words {two fp16, epoch} of even / odd epochs (one-kernel protocol)
 constexpr int kGatherMaxRanks = 8;
 constexpr int kGatherCtrlBytes = 1024;
-constexpr int kGatherEpochOff = 0, kGatherDoneOff = 4, kGatherErrorOff = 8, kGatherTicketOff = 12, kGatherFlagsOff = 64,
-              kGatherArrivalsOff = 128;
+constexpr int kGatherEpochOff = 0, kGatherDoneOff = 4, kGatherErrorOff = 8, kGatherTicketOff = 12, kGatherFlagsOff = 64;
 constexpr int kGatherWaitCtas = 8;  // fixed grid of the wait kernel: its call number is tickets / 8
 
 struct GatherTable {

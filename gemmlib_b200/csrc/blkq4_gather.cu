@@ -100,7 +100,7 @@ extern "C" int blkq4_gather_create(int world, int rank, size_t max_out_bytes, vo
   c->world = world;
   c->rank = rank;
   c->buf_bytes = (max_out_bytes + 255) & ~(size_t)255;
-  c->block_bytes = blkq4::kGatherCtrlBytes + 2 * c->buf_bytes;
+  c->block_bytes = blkq4::kGatherCtrlBytes + 6 * c->buf_bytes;  // two fp16 buffers + two buffers of flagged words
   void* p = nullptr;
   cudaError_t e = cudaMalloc(&p, c->block_bytes);
   if (e == cudaSuccess) e = cudaMemset(p, 0, c->block_bytes);

@@ -67,13 +67,13 @@ struct StreamParams {
 
 constexpr long long kGatherWaitCycles = 2000000000ll;  // ~1 s
 
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint2 ld_relaxed_sys_v2(const void* p) {
+  uint2 v;
+  asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void red_release_sys_add(unsigned* p, unsigned v) {
-  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_sys_v2(void* p, uint32_t x, uint32_t y) {
+  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(x), "r"(y) : "memory");
 }
 
 __device__ __forceinline__ uint32_t lop3_and_or(uint32_t x, uint32_t mask, uint32_t bits) {
@@ -147,14 +147,15 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 //                | s_part [2][PW][16][MS] | s_stage [8][16] fp16 (gather) | s_a [M][a_pitch]
 // MZ: rows of the zero-point accumulators kept in registers (2 for M <= 2, else 8).
 //
-// GATHER (N-sharded layer, one process per GPU): the adding warp stores the tile's fp16 results into
-// EVERY rank's gathered buffer with 16-byte peer stores; when a CTA has stored its last tile it adds
-// one to this rank's arrival counter in every rank's block (red.release.sys); then every CTA waits -
-// bounded - until the counters of all ranks have reached the grid size, copies its share of the
-// complete [M, world * N] result to `out`, and the last CTA re-arms the counters and advances the
-// epoch.  One launch per layer; nothing polls from a second kernel.  Epochs alternate between two
-// buffers and two counter sets: a peer reaches epoch e + 2 only after this rank's arrivals of epoch
-// e + 1, which follow (stream order) the completion of this rank's launch of epoch e.
+// GATHER (N-sharded layer, one process per GPU).  The exchange is latency-bound (a few tens of KB per
+// rank), so it carries its own flags: the adding warp stores the tile's results into EVERY rank's
+// exchange buffer as 8-byte words {two fp16 results, the call's epoch} - an aligned 8-byte store
+// arrives whole, so a word whose flag equals the epoch holds that epoch's data and no fence, counter
+// or second flag flight is needed.  When a CTA has finished its tiles it turns receiver: its threads
+// poll - bounded - their share of the words of the complete [M, world * N] result in this rank's
+// buffer and write the data halves to `out`.  The last CTA advances the rank's epoch.  One launch per
+// layer.  Epochs alternate between two buffers: a peer writes epoch e + 2 only after it has received
+// this rank's words of epoch e + 1, which this rank sends after its launch of epoch e has completed.
 template <bool HAS_ZP, int D, int MZ, bool GATHER>
 __global__ void __launch_bounds__(kWarps * 32, 2)
 gemv_stream_kernel(const StreamParams p) {
@@ -244,7 +245,7 @@ gemv_stream_kernel(const StreamParams p) {
   size_t gather_off = 0;
   if (GATHER) {
     gather_epoch = *reinterpret_cast<volatile unsigned*>(p.gt.base[p.gt.rank] + kGatherEpochOff) + 1u;
-    gather_off = kGatherCtrlBytes + (size_t)(gather_epoch & 1u) * p.gt.buf_bytes;
+    gather_off = kGatherCtrlBytes + (size_t)(2 + 2 * (gather_epoch & 1u)) * p.gt.buf_bytes;  // flagged-word buffers follow the two fp16 ones
   }
 
   // ---- per warp: its own K slice of the activations into shared memory, and the activation-only
@@ -396,14 +397,13 @@ gemv_stream_kernel(const StreamParams p) {
         else p.out[(size_t)m * N + n] = p.bias ? __hadd(h, p.bias[n]) : h;
       }
       if (GATHER) {
-        // this rank's 16 columns of row m, as two 16-byte pieces, into every rank's gathered buffer
+        // this rank's 16 columns of row m as eight flagged words, into every rank's buffer
         __syncwarp();
-        if (lane < 2 * M) {
-          const int m = lane >> 1, piece = lane & 1;
-          const uint4 v = *reinterpret_cast<const uint4*>(s_stage + m * 16 + piece * 8);
-          const size_t off = gather_off +
-              ((size_t)m * p.gt.n_total + (size_t)p.gt.rank * N + (size_t)tile * 16 + piece * 8) * sizeof(__half);
-          for (int r = 0; r < p.gt.world; ++r) *reinterpret_cast<uint4*>(p.gt.base[r] + off) = v;
+        for (int w = lane; w < 8 * M; w += 32) {
+          const int m = w >> 3, pair = w & 7;
+          const uint32_t data = *reinterpret_cast<const uint32_t*>(s_stage + m * 16 + pair * 2);
+          const size_t word = ((size_t)m * p.gt.n_total + (size_t)p.gt.rank * N + (size_t)tile * 16) / 2 + pair;
+          for (int r = 0; r < p.gt.world; ++r) st_relaxed_sys_v2(p.gt.base[r] + gather_off + word * 8, data, gather_epoch);
         }
         __syncwarp();
       }
@@ -412,42 +412,34 @@ gemv_stream_kernel(const StreamParams p) {
   cp_async_wait<0>();
   if (GATHER) {
     uint8_t* local = p.gt.base[p.gt.rank];
-    const unsigned slot = gather_epoch & 1u;
-    // every adding warp's peer stores are ordered before the barrier; one thread publishes them
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      __threadfence_system();
-      const size_t aoff = kGatherArrivalsOff + ((size_t)slot * kGatherMaxRanks + p.gt.rank) * sizeof(unsigned);
-      for (int r = 0; r < p.gt.world; ++r) red_release_sys_add(reinterpret_cast<unsigned*>(p.gt.base[r] + aoff), 1u);
-    }
-    // wait, bounded, for every rank's CTAs (all ranks launch the same grid)
-    if ((int)threadIdx.x < p.gt.world) {
-      const unsigned* ctr = reinterpret_cast<const unsigned*>(local + kGatherArrivalsOff) + slot * kGatherMaxRanks + threadIdx.x;
-      const long long t0 = clock64();
-      while (ld_acquire_sys(ctr) < gridDim.x) {
-        if (clock64() - t0 > kGatherWaitCycles) {
-          atomicCAS(reinterpret_cast<int*>(local + kGatherErrorOff), 0, 0x400 | (int)threadIdx.x);
-          break;
+    // receiver: this CTA's share of the words of the complete result
+    const unsigned long long nwords = (unsigned long long)M * p.gt.n_total / 2;
+    const uint8_t* src = local + gather_off;
+    uint32_t* dst = reinterpret_cast<uint32_t*>(p.out);
+    bool expired = false;
+    for (unsigned long long i = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; i < nwords;
+         i += (unsigned long long)gridDim.x * blockDim.x) {
+      uint2 w = ld_relaxed_sys_v2(src + i * 8);
+      if (w.y != gather_epoch && !expired) {
+        const long long t0 = clock64();
+        while ((w = ld_relaxed_sys_v2(src + i * 8)).y != gather_epoch) {
+          if (clock64() - t0 > kGatherWaitCycles) {
+            // which rank's columns are missing: word i covers columns 2 (i % (n_total / 2)), + 1
+            const int col = (int)(i % (unsigned long long)(p.gt.n_total / 2)) * 2;
+            atomicCAS(reinterpret_cast<int*>(local + kGatherErrorOff), 0, 0x400 | (col / N));
+            expired = true;  // this thread stops waiting for its other words too
+            break;
+          }
         }
       }
+      if (w.y == gather_epoch) dst[i] = w.x;
     }
     __syncthreads();
-    // copy this CTA's share of the complete result out (peers wrote it over NVLink: read around L1)
-    const unsigned long long n16 = (unsigned long long)M * p.gt.n_total * sizeof(__half) / 16;
-    const uint4* src = reinterpret_cast<const uint4*>(local + gather_off);
-    uint4* dst = reinterpret_cast<uint4*>(p.out);
-    for (unsigned long long i = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; i < n16;
-         i += (unsigned long long)gridDim.x * blockDim.x)
-      dst[i] = __ldcg(src + i);
-    __syncthreads();
     if (threadIdx.x == 0) {
-      __threadfence();
       const unsigned arrived = atomicAdd(reinterpret_cast<unsigned*>(local + kGatherDoneOff), 1u);
       if (arrived == gridDim.x - 1) {
-        // last CTA of this rank: re-arm this slot's counters, keep the two-kernel protocol's ticket
-        // numbering in step (its wait kernel draws kGatherWaitCtas tickets per call), advance the epoch
-        unsigned* ctrs = reinterpret_cast<unsigned*>(local + kGatherArrivalsOff) + slot * kGatherMaxRanks;
-        for (int r = 0; r < kGatherMaxRanks; ++r) ctrs[r] = 0u;
+        // last CTA of this rank: keep the two-kernel protocol's ticket numbering in step (its wait
+        // kernel draws kGatherWaitCtas tickets per call) and advance the epoch
         *reinterpret_cast<volatile unsigned*>(local + kGatherDoneOff) = 0u;
         atomicAdd(reinterpret_cast<unsigned*>(local + kGatherTicketOff), (unsigned)kGatherWaitCtas);
         __threadfence();

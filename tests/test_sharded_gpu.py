@@ -20,7 +20,7 @@ pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
 
 
-@pytest.mark.parametrize("M,has_zp,block", [(1, False, 64), (4, True, 64), (16, False, 128)])
+@pytest.mark.parametrize("M,has_zp,block", [(1, False, 64), (4, True, 64), (7, True, 128), (8, False, 64), (16, False, 128)])
 def test_world_size_one_fused_gather_matches_plain(M, has_zp, block):
     from gemmlib_b200.ms_blkq4linear import BlkQ4Linear
     from gemmlib_b200.sharded import PeerGather
