@@ -120,6 +120,8 @@ def cpu_dequant_gemm_sample(cfg, min_seconds=10.0, max_seconds=25.0):
 
     from oracle import blkq4_oracle as O
 
+    # launchers such as torchrun export OMP_NUM_THREADS=1: the CPU arm uses every core it may run on
+    O.set_num_threads(O.host_cores())
     g = torch.Generator().manual_seed(0)
     w = (torch.randn(cfg["N"], cfg["K"], generator=g) * cfg["sigma"]).to(torch.float16).numpy()
     a = torch.randn(cfg["M"], cfg["K"], generator=g).to(torch.float16).numpy()
@@ -171,8 +173,9 @@ def workload_config(n_gpus):
     return {
         "workload": "c2 decode GEMV: M=1 K=4096 N=11008 block=64 column-wise symmetric, fp16 scales"
                     + (f"; N-sharded x{n_gpus}: each rank owns one c2-sized shard; the all-gather of every layer's "
-                       "outputs is fused into the kernel (peer stores over NVLink + flag wait)" if n_gpus > 1 else ""),
-        "launches_per_step": LAYERS * (2 if n_gpus > 1 else 1),
+                       "outputs is fused into the kernel (flagged peer stores over NVLink, in-kernel wait and copy-out)"
+                       if n_gpus > 1 else ""),
+        "launches_per_step": LAYERS,
         "l2": f"inputs larger than L2: a step walks {LAYERS} layers with distinct weights ({LAYERS} x 24 MB > 126 MB)",
         "parallelism": f"n-shard{n_gpus}" if n_gpus > 1 else "single",
     }
@@ -358,6 +361,35 @@ def run_ours(args):
     e2e_value = nbytes * LAYERS * e2e_steps * world / (e2e_ms * 1e-3) / 1e9
     _log("end-to-end region done")
 
+    e2e_stack = None
+    if world == 1:
+        # the same pass through LinearStack: one pinned-host -> device copy, ONE graph replay, results back
+        from gemmlib_b200.stack import LinearStack
+
+        stk = LinearStack([(lyr, "x", "y%d" % i) for i, lyr in enumerate(layers)])
+        bufs = stk.buffers(M)
+        out_host_all = torch.empty(LAYERS, M, N, dtype=torch.float16).pin_memory()
+
+        def step_stack():
+            bufs["x"].copy_(a_host, non_blocking=True)
+            stk.replay(M)
+            for i in range(LAYERS):
+                out_host_all[i].copy_(bufs["y%d" % i], non_blocking=True)
+
+        for _ in range(3):
+            step_stack()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(e2e_steps):
+            step_stack()
+        e1.record()
+        torch.cuda.synchronize()
+        stack_ms = e0.elapsed_time(e1)
+        e2e_stack = {"value": round(nbytes * LAYERS * e2e_steps / (stack_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
+                     "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": LAYERS * M * N * 2,
+                     "api": "LinearStack.replay: one activation copy in, one CUDA graph over the 16 layers, 16 result copies out"}
+        torch.cuda.synchronize()
+
     line = {
         "metric": "W4A16 effective HBM GB/s (M<=16)", "value": round(value, 2), "unit": "GB/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -367,9 +399,11 @@ def run_ours(args):
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": LAYERS * M * K * 2,
                 "d2h_bytes_per_step": LAYERS * M * N * world * 2, "steps": e2e_steps,
                 "api": "BlkQ4Linear.forward(x, out=), pinned host activation copied in, result copied to pinned host memory, per layer"},
-        "gpu_launches": args.steps * LAYERS * (2 if (world > 1 and fused) else 1),
+        "gpu_launches": args.steps * LAYERS,  # one kernel of this library per layer (fused exchange included)
         "kernel_status": status,
     }
+    if e2e_stack is not None:
+        line["e2e_stack"] = e2e_stack
     if world > 1:
         # same layers, unfused: skinny kernel + NCCL all-gather per layer, graph replay
         for _ in range(2):
@@ -395,6 +429,12 @@ def run_ours(args):
         line["gather_status"] = peer.status() if peer is not None else None
         line["exchange"] = "fused into the kernel" if fused else "NCCL all-gather (" + fused_note + ")"
         del g2
+        if not args.skip_extras:
+            try:
+                line["c4_sharded"] = bench_c4_sharded(torch, dist, dev, peaks, world, rank,
+                                                      (lambda rows, n: PeerGather(rows, n)) if fused else (lambda rows, n: None))
+            except Exception as exc:  # an extra must never cost the headline
+                line["c4_sharded"] = {"unavailable": "%s: %s" % (type(exc).__name__, exc)}
     if rank == 0:
         sampler_summary = None
         time.sleep(0.15)
@@ -407,7 +447,7 @@ def run_ours(args):
         line["roofline"] = {
             "bound": "hbm", "achieved": round(nbytes / (launch_us * 1e-6) / 1e9, 2), "peak": peaks["hbm_gbs"],
             "unit": "GB/s", "frac": round(nbytes / (launch_us * 1e-6) / 1e9 / peaks["hbm_gbs"], 4),
-            "traffic": TRAFFIC_BYTES_PER_LAUNCH, "kernel": "gemv_persistent_kernel<1,false>",
+            "traffic": TRAFFIC_BYTES_PER_LAUNCH, "kernel": "gemv_stream_kernel<false,4,2,false>",
             "bytes_per_launch": nbytes, "us_per_launch": round(launch_us, 3), "peak_source": peaks["source"],
         }
     if world == 1 and not args.skip_extras:
@@ -626,6 +666,76 @@ def bench_reference_gpu(torch, dev, layers_c2, a_dev):
     return out
 
 
+
+def bench_c5_quant(torch, dev, peaks):
+    """Quantize + prepack of the 224 layers of configs[4] (block 64, zero points): this library's one
+    fused kernel per layer, timed per layer shape over fp16 sources that rotate through more than L2,
+    and the reference's own path (three kernels between three cudaMalloc / cudaFree,
+    src/blkq4_f16_gemm_sm80.cu:282-303, from oracle/_ref) on one layer of each shape."""
+    import ctypes
+
+    from gemmlib_b200 import capi
+
+    shapes = [("4096->4096", 4096, 4096, 4 * 32), ("4096->11008", 4096, 11008, 2 * 32), ("11008->4096", 11008, 4096, 32)]
+    block = 64
+    ref = None
+    path = os.path.join(ROOT, "oracle", "_ref", "libms_blkq4gemm_ref.so")
+    if os.path.exists(path):
+        ref = ctypes.CDLL(path)
+        vp, sz = ctypes.c_void_p, ctypes.c_size_t
+        ref.blkq4_fp16_quant_sm80.argtypes = [ctypes.c_int, ctypes.c_bool] + [ctypes.c_int] * 3 + [vp] + [vp, sz] * 4 + [vp]
+        ref.blkq4_fp16_quant_sm80.restype = ctypes.c_int
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    rows, total_us, total_bytes, ref_total_us = [], 0.0, 0, 0.0
+    for name, K, N, count in shapes:
+        wb, me = capi.quant_size(block, True, K, N)
+        nsrc = max(2, -(-300_000_000 // (2 * K * N)))
+        srcs = [(torch.randn(N, K, device=dev) * 0.02).half() for _ in range(nsrc)]
+        qw = torch.empty(wb, dtype=torch.uint8, device=dev)
+        qs = torch.empty(me, dtype=torch.float16, device=dev)
+        qz = torch.empty(me, dtype=torch.uint8, device=dev)
+        for w in srcs:
+            capi.quant(block, True, K, N, K, w, qw, qs, qz)
+        torch.cuda.synchronize()
+        reps = 5
+        e0.record()
+        for _ in range(reps):
+            for w in srcs:
+                capi.quant(block, True, K, N, K, w, qw, qs, qz)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (reps * nsrc)
+        nbytes = 2 * K * N + K * N // 2 + 2 * me + me
+        row = {"layer": name, "count": count, "us_per_layer": round(us, 2), "GB/s": round(nbytes / us / 1e3, 1),
+               "frac_of_hbm": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 4)}
+        if ref is not None:
+            # the reference allocates and frees inside the call (an implicit device sync): wall clock
+            def ref_call(w):
+                rc = ref.blkq4_fp16_quant_sm80(block, True, K, N, K, None, w.data_ptr(), w.numel() * 2, qw.data_ptr(), wb,
+                                               qs.data_ptr(), me * 2, qz.data_ptr(), me, None)
+                if rc != 0:
+                    raise RuntimeError("reference quantizer returned %d" % rc)
+            ref_call(srcs[0])
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for w in srcs:
+                ref_call(w)
+            torch.cuda.synchronize()
+            rus = (time.perf_counter() - t0) * 1e6 / nsrc
+            row["reference_us_per_layer"] = round(rus, 2)
+            ref_total_us += rus * count
+        rows.append(row)
+        total_us += us * count
+        total_bytes += nbytes * count
+        del srcs
+    out = {"ms_all_224_layers": round(total_us / 1e3, 3), "GB/s": round(total_bytes / total_us / 1e3, 1),
+           "frac_of_hbm": round(total_bytes / total_us / 1e3 / peaks["hbm_gbs"], 4), "bytes": total_bytes, "per_shape": rows}
+    if ref is not None:
+        out["reference_ms_all_224_layers"] = round(ref_total_us / 1e3, 3)
+        out["reference_what"] = "reference CUDA quantizer (3 kernels + 3 cudaMalloc/cudaFree per call) compiled for sm_100a, wall clock"
+    return out
+
+
 def bench_c5_stack(torch, dev, peaks):
     """configs[4]: the 224 linears of a Llama-2-7B-shaped decoder (32 x {q,k,v,o: 4096->4096;
     gate,up: 4096->11008; down: 11008->4096}), block 64 with zero points, random weights,
@@ -641,6 +751,10 @@ def bench_c5_stack(torch, dev, peaks):
     st = llama_like_stack(4096, 11008, 32, 64, True, False, dev, weight_fn=weight_fn)
     out = {"workload": "c5: 224 linears (32 Llama-2-7B-shaped blocks), block 64 zero points, one CUDA graph per M",
            "linears": st.num_linears}
+    try:
+        out["quantize_prepack_all_layers"] = bench_c5_quant(torch, dev, peaks)
+    except Exception as exc:
+        out["quantize_prepack_all_layers"] = {"unavailable": "%s: %s" % (type(exc).__name__, exc)}
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for M, reps in ((1, 50), (512, 10)):
         st.buffers(M)["x"].copy_(torch.randn(M, 4096, generator=gen, device=dev).to(torch.float16))
@@ -664,6 +778,89 @@ def bench_c5_stack(torch, dev, peaks):
             out["prefill_M512"] = {"ms_per_pass": round(ms, 4), "TFLOP/s": round(tf, 1),
                                    "frac_of_tensor": round(tf / peaks["tflops"], 4)}
     return out
+
+
+
+NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction per GPU on this pool (nominal 900)
+
+
+def bench_c4_sharded(torch, dist, dev, peaks, world, rank, peer_factory):
+    """configs[3] sharded: K=8192, N=28672 split along N over the ranks (block 128, symmetric), every
+    rank ends with the full [M, N].  Per M: the local shard alone ("compute") and the whole layer
+    ("end_to_end": fused kernel + exchange for M <= 16, tensor-core kernel + NCCL all-gather above),
+    with the bound max(HBM time, tensor time, NVLink time of (g-1)/g * 2MN bytes into each GPU)."""
+    from gemmlib_b200.ms_blkq4linear import BlkQ4Linear
+    from gemmlib_b200.sharded import gather_columns
+
+    K, N, block = 8192, 28672, 128
+    ns = N // world
+    shard_bytes = K * ns // 2
+    nsets = max(2, min(24, -(-300_000_000 // shard_bytes)))  # distinct weight sets: more than L2 in total
+    gen = torch.Generator(device=dev).manual_seed(70 + rank)
+    layers = [BlkQ4Linear(block, True, True, (torch.randn(ns, K, generator=gen, device=dev) * 0.015).to(torch.float16))
+              for _ in range(nsets)]
+    peer = peer_factory(16, N)
+    stream = torch.cuda.Stream()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    rows = []
+
+    def timed(fn, reps):
+        with torch.cuda.stream(stream):
+            for _ in range(2):
+                fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            fn()
+        graph.replay()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0.record()
+        for _ in range(reps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) * 1e3 / (reps * nsets)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        del graph
+        return float(t.item())
+
+    for M in (1, 16, 256, 4096):
+        x = torch.randn(M, K, generator=torch.Generator(device=dev).manual_seed(7), device=dev).to(torch.float16)
+        shard_out = torch.empty(M, ns, dtype=torch.float16, device=dev)
+        full = torch.empty(M, N, dtype=torch.float16, device=dev)
+        use = layers if M <= 256 else layers[:2]
+        reps = 10 if M <= 256 else 3
+
+        def compute():
+            for lyr in use:
+                lyr(x, out=shard_out)
+
+        def e2e():
+            for lyr in use:
+                if M <= 16 and peer is not None:
+                    peer.forward(lyr, x, full, flags=1)
+                else:
+                    gather_columns(lyr(x, out=shard_out))
+
+        scale = nsets / len(use)
+        us_c = timed(compute, reps) * scale
+        us_e = timed(e2e, reps) * scale
+        nbytes = algorithmic_bytes(M, K, ns, block, True, False)
+        flops = 2.0 * M * ns * K
+        t_hbm, t_tc = nbytes / (peaks["hbm_gbs"] * 1e3), flops / (peaks["tflops"] * 1e6)
+        t_link = (world - 1) / world * 2.0 * M * N / (NVLINK_GBS * 1e3)
+        bound = max(t_hbm, t_tc, t_link)
+        rows.append({"M": M, "compute_us": round(us_c, 2), "end_to_end_us": round(us_e, 2),
+                     "bound_us": round(bound, 2), "bound": "hbm" if bound == t_hbm else ("tensor" if bound == t_tc else "nvlink"),
+                     "compute_frac": round(max(t_hbm, t_tc) / us_c, 4), "end_to_end_frac": round(bound / us_e, 4),
+                     "exchange": "fused in the kernel" if (M <= 16 and peer is not None) else "NCCL all-gather"})
+    if peer is not None:
+        torch.cuda.synchronize()
+        dist.barrier()
+        peer.close()
+    return {"workload": f"c4 sharded x{world}: K=8192 N=28672/{world} block 128 symmetric, {nsets} weight sets per rank",
+            "rows": rows}
 
 
 def bench_c4_sweep(torch, dev, peaks):

@@ -57,6 +57,15 @@ int blkq4_oracle_num_threads(void) {
 #endif
 }
 
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; a timed baseline sets its thread count itself. */
+void blkq4_oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 /* ------------------------------------------------------------------------- */
 /* Shape rules.  Reference: src/blkq4_f16_gemm_sm80.cu:155-203 (K % 64, N % 32,
  * empty problem) and f16_quant_sm80.cuh:190-198 (sizes).  Block 128 is accepted

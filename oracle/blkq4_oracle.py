@@ -52,6 +52,21 @@ def num_threads() -> int:
     return int(_lib.blkq4_oracle_num_threads())
 
 
+def set_num_threads(n: int) -> int:
+    """Set the OpenMP thread count of the oracle's loops (launchers may have exported
+    OMP_NUM_THREADS=1); returns the count now in effect."""
+    _lib.blkq4_oracle_set_num_threads(int(n))
+    return num_threads()
+
+
+def host_cores() -> int:
+    """Cores this process may run on."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def blocking(block: int, colwise: bool):
     return (block, 1) if colwise else (1, block)
 
