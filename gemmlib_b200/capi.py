@@ -34,6 +34,8 @@ SYMBOLS = (
     "blkq4_fp16_gemm_gather_sm100",
     "blkq4_gather_status",
     "blkq4_gather_destroy",
+    "blkq4_gather_reset",
+    "blkq4_reset",
     "blkq4_version",
 )
 
@@ -75,6 +77,10 @@ def _load() -> ctypes.CDLL:
     lib.blkq4_version.restype = ctypes.c_char_p
     lib.blkq4_last_kernel_status.argtypes = [vp]
     lib.blkq4_last_kernel_status.restype = i
+    lib.blkq4_gather_reset.argtypes = [vp]
+    lib.blkq4_gather_reset.restype = i
+    lib.blkq4_reset.argtypes = [vp]
+    lib.blkq4_reset.restype = i
     lib.blkq4_gather_create.argtypes = [i, i, sz, ctypes.POINTER(vp), vp, vp]
     lib.blkq4_gather_create.restype = i
     lib.blkq4_gather_connect.argtypes = [vp, vp, vp]
@@ -210,6 +216,12 @@ def gemm(block_size, column_wise, m, n, k, act, q_weights, q_scales, q_zp, out, 
             raise BlkQ4Error(e.text())
 
 
+def reset(stream=0) -> None:
+    """Clear the kernels' status words and the static scratch's flag words (``blkq4_reset``)."""
+    if lib.blkq4_reset(stream) != 0:
+        raise BlkQ4Error("blkq4_reset failed")
+
+
 class GatherContext:
     """One rank's side of the fused GEMM + all-gather (``blkq4_gather_*``).
 
@@ -262,12 +274,30 @@ class GatherContext:
         return int(lib.blkq4_gather_status(self._ctx, stream))
 
     def close(self):
+        """Unmap the peers' blocks and free this rank's.  With more than one rank the caller must
+        first have drained every rank's stream and passed a cross-rank barrier (PeerGather.close
+        does both): peers store into this block from their own kernels."""
         if self._ctx:
             lib.blkq4_gather_destroy(self._ctx)
             self._ctx = ctypes.c_void_p()
 
+    def reset(self):
+        """After a wait that expired (status() != 0): clear the error word and the control words of
+        this rank's block.  Collective in effect: every rank resets between the same two calls, with
+        all streams drained."""
+        if self._ctx and lib.blkq4_gather_reset(self._ctx) != 0:
+            raise BlkQ4Error("blkq4_gather_reset failed")
+
     def __del__(self):
+        # A garbage-collected context must not free memory that peers may still be storing into:
+        # with several ranks only an explicit, ordered close() does that.
         try:
-            self.close()
+            if self.world <= 1:
+                self.close()
+            elif self._ctx:
+                import warnings
+
+                warnings.warn("GatherContext of a multi-rank exchange was dropped without close(); "
+                              "its device block is left allocated", ResourceWarning)
         except Exception:
             pass

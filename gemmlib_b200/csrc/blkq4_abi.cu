@@ -146,6 +146,12 @@ extern "C" int blkq4_fp16_gemm_ws_sm100(int block_size, bool column_wise_blockin
       reinterpret_cast<uintptr_t>(scales_ptr) % 2 != 0)
     return fail(err, "Kernel execution failed: Error Misaligned Operand");
 
+  // The tensor-core kernel fetches scales and zero points with TMA (16-byte aligned bases; the skinny
+  // kernels fall back to plain loads instead).
+  if (m > 16 && (reinterpret_cast<uintptr_t>(scales_ptr) % 16 != 0 ||
+                 (has_offsets && reinterpret_cast<uintptr_t>(offsets_ptr) % 16 != 0)))
+    return fail(err, "Kernel execution failed: Error Misaligned Operand (scales and offsets must be 16-byte aligned for m > 16)");
+
   auto stream = reinterpret_cast<cudaStream_t>(stream_ptr);
   auto a = reinterpret_cast<const __half*>(act_ptr);
   auto w = reinterpret_cast<const uint8_t*>(weights_ptr);
@@ -204,5 +210,13 @@ extern "C" int blkq4_last_kernel_status(void* stream_ptr) {
   if (tc != 0) return tc;
   const int gv = blkq4::read_gemv_error();
   return gv > 0 ? (0x10000 | gv) : gv;
+}
+extern "C" int blkq4_reset(void* stream_ptr) {
+  auto stream = reinterpret_cast<cudaStream_t>(stream_ptr);
+  int rc = 0;
+  rc |= blkq4::clear_gemm_tc_error(stream);
+  rc |= blkq4::clear_gemv_error(stream);
+  rc |= blkq4::reset_static_scratch(stream);
+  return rc == 0 ? 0 : -1;
 }
 extern "C" char const* blkq4_version(void) { return "gemmlib_b200 0.1 sm_100a"; }

@@ -84,6 +84,10 @@ size_t gemm_tc_workspace_bytes(int M, int N, int K);
 int read_gemm_tc_error(cudaStream_t stream);
 // The skinny kernel's device error word (call after the stream has been synchronised).
 int read_gemv_error();
+// Recovery after an expired wait: clear the kernels' error words / the static scratch's flag words.
+int clear_gemm_tc_error(cudaStream_t stream);
+int clear_gemv_error(cudaStream_t stream);
+int reset_static_scratch(cudaStream_t stream);
 
 #ifdef __CUDACC__
 

@@ -226,6 +226,15 @@ extern "C" int blkq4_gather_status(void* ctx, void* stream_ptr) {
   return v;
 }
 
+extern "C" int blkq4_gather_reset(void* ctx) {
+  auto* c = reinterpret_cast<GatherCtx*>(ctx);
+  if (!c) return -1;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  // control words only: the epoch restarts at zero on every rank, the buffers' stale flags (all
+  // smaller than or equal to the old epoch) would be taken for fresh data, so they go too
+  return cudaMemset(c->base[c->rank], 0, c->block_bytes) == cudaSuccess ? 0 : -1;
+}
+
 extern "C" int blkq4_gather_destroy(void* ctx) {
   auto* c = reinterpret_cast<GatherCtx*>(ctx);
   if (!c) return 0;

@@ -707,6 +707,12 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
   return std::string();
 }
 
+int clear_gemm_tc_error(cudaStream_t stream) {
+  void* p = nullptr;
+  if (cudaGetSymbolAddress(&p, g_gemm_tc_error) != cudaSuccess) return -1;
+  return cudaMemsetAsync(p, 0, sizeof(int), stream) == cudaSuccess ? 0 : -1;
+}
+
 int read_gemm_tc_error(cudaStream_t stream) {
   int v = 0;
   if (cudaStreamSynchronize(stream) != cudaSuccess) return -1;

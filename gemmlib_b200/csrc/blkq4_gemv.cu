@@ -768,6 +768,12 @@ int sm_count() {
   return sms;
 }
 
+int clear_gemv_error(cudaStream_t stream) {
+  void* p = nullptr;
+  if (cudaGetSymbolAddress(&p, g_gemv_error) != cudaSuccess) return -1;
+  return cudaMemsetAsync(p, 0, sizeof(int), stream) == cudaSuccess ? 0 : -1;
+}
+
 int read_gemv_error() {
   int v = 0;
   if (cudaMemcpyFromSymbol(&v, g_gemv_error, sizeof(int)) != cudaSuccess) return -1;

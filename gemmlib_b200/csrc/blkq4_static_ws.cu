@@ -13,8 +13,10 @@
 
 namespace {
 
-// 12 MiB: enough for every split the planner makes at M <= 512 on 4096-wide layers (8.4 MB) and
-// for a 148-SM part's largest two-way split (74 tiles x 128 KB = 9.7 MB); larger plans are refused.
+// 12 MiB.  Covers, e.g., M = 512 on 4096-wide layers (64 tiles, two-way split: 8.4 MB) and a 148-SM
+// part's largest two-way split at BM = 256 (74 tiles x 128 KB = 9.7 MB).  A problem whose preferred
+// plan needs more - e.g. M = 256, N = K = 4096: 32 tiles split four ways, 12.6 MB - is refused; call
+// blkq4_fp16_gemm_sm100 (no split) or blkq4_fp16_gemm_ws_sm100 with memory of your own for those.
 constexpr size_t kStaticScratchBytes = 12u << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
@@ -52,6 +54,18 @@ void* static_scratch(std::string& why) {
 }  // namespace
 
 extern "C" size_t blkq4_static_scratch_size(void) { return kStaticScratchBytes; }
+
+namespace blkq4 {
+// Zeroes the flag words at the head of the static scratch on the current device (the partial tiles
+// behind them need no clearing).  Enqueued on `stream`; allocates nothing.
+int reset_static_scratch(cudaStream_t stream) {
+  std::string why;
+  void* scratch = static_scratch(why);
+  if (!scratch) return -1;
+  // flags: one word per output tile, at most one tile per SM and split; 64 KB is far beyond any plan
+  return cudaMemsetAsync(scratch, 0, 64 * 1024, stream) == cudaSuccess ? 0 : -1;
+}
+}  // namespace blkq4
 
 extern "C" int blkq4_fp16_gemm_static_ws_sm100(int block_size, bool column_wise_blocking, int m, int n, int k,
                                                void* stream, void const* act_ptr, size_t a_size,

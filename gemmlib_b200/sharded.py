@@ -112,7 +112,17 @@ class PeerGather:
         return self.ctx.status()
 
     def close(self):
+        """Collective: every rank drains its device, then all meet at a barrier, and only then are the
+        exchange blocks unmapped and freed - a peer's kernel may store into this rank's block until
+        that peer has drained.  Safe to call twice."""
+        if getattr(self, "ctx", None) is None:
+            return
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        if self.world > 1 and dist.is_initialized():
+            dist.barrier(self.group)
         self.ctx.close()
+        self.ctx = None
 
 
 class ShardedBlkQ4Linear(nn.Module):
@@ -160,10 +170,16 @@ class ShardedBlkQ4Linear(nn.Module):
             if self.bias is not None:
                 full += self.bias
             return full.view(*lead, self.out_features)
-        out = self.local(x)
-        if self.gather_output:
-            out = gather_columns(out, self.group)
-            if self.bias is not None:
-                out += self.bias
+        if not self.gather_output:
+            # the caller's buffer, if any, receives this rank's columns
+            local_out = None if out is None else out.view(-1, self.local.out_features)
+            res = self.local(x, out=local_out)
+            return res.view(*lead, -1)
+        res = gather_columns(self.local(x), self.group)
+        if self.bias is not None:
+            res += self.bias
+        if out is not None:
+            # a caller that reads its own buffer (a captured graph, a LinearStack) must find the result there
+            out.view(-1, self.out_features).copy_(res)
             return out.view(*lead, self.out_features)
-        return out.view(*lead, -1)
+        return res.view(*lead, self.out_features)

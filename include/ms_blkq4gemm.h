@@ -167,8 +167,13 @@ int blkq4_fp16_gemm_ws_sm100(
  * blkq4_fp16_gemm_ws_sm100 with the workspace taken from a 12 MiB device array that is part of the
  * library (blkq4_static_scratch_size() bytes) instead of from the caller: nothing on this path
  * allocates, on the host or on the device.  A problem whose split-K workspace
- * (blkq4_gemm_workspace_size) would not fit is refused with an error; one call at a time per
- * device may use the array.  No counterpart in the reference.
+ * (blkq4_gemm_workspace_size) would not fit is refused with an error (e.g. M = 256, N = K = 4096:
+ * 32 tiles split four ways need 12.6 MB); use blkq4_fp16_gemm_sm100 for it.  Every call on a
+ * device shares the one array, so calls that can overlap on the GPU - on different streams, or
+ * replays of captured graphs running side by side - race and corrupt each other's results: one
+ * call at a time per device.  If a bounded in-kernel wait expires (blkq4_last_kernel_status != 0),
+ * per-tile flag words may be left set in the array; blkq4_reset() clears them.  No counterpart in
+ * the reference.
  */
 size_t blkq4_static_scratch_size(void);
 int blkq4_fp16_gemm_static_ws_sm100(
@@ -190,19 +195,25 @@ int blkq4_fp16_gemm_static_ws_sm100(
  *
  * Rank r holds the weight columns [r*n_shard, (r+1)*n_shard).  blkq4_gather_create allocates the
  * rank's exchange block (the one place this library allocates device memory: 1 KB of control
- * words plus two buffers of max_out_bytes) and returns its 64-byte CUDA IPC handle; the caller
+ * words plus six buffers of max_out_bytes) and returns its 64-byte CUDA IPC handle; the caller
  * exchanges the handles of all ranks by any means (e.g. its process group) and passes them,
  * ordered by rank, to blkq4_gather_connect.  blkq4_fp16_gemm_gather_sm100 then computes this
  * rank's [m, n_shard] slice and delivers the complete [m, world*n_shard] result into
- * output_ptr on EVERY rank: the kernel's epilogue stores the slice into all ranks' exchange
- * buffers over NVLink and raises a per-rank flag; a second small kernel waits (bounded, ~1 s)
- * for all flags and copies the gathered rows out.  All ranks must make the same sequence of
- * calls; work that reads output_ptr must be enqueued on `stream` before the next gather call.
- * A shape outside the skinny kernel's TMA fast path (column-wise, block >= 64, 512 <= K <= 32768,
- * M <= 16) is refused with an error text starting "Kernel execution failed: unsupported":
- * compute with blkq4_fp16_gemm_sm80 and all-gather with the caller's collective instead.
- * blkq4_gather_status synchronises `stream` and returns 0, or (0x400 | rank) of the first
- * rank whose flag did not arrive in time.
+ * output_ptr on EVERY rank.  Decode shapes (m <= 8, K a multiple of 256, K >= 2048) take ONE
+ * launch: the kernel stores its results into all ranks' exchange buffers over NVLink as 8-byte
+ * words that carry the call's number, then waits (bounded, ~1 s) for the words of all ranks and
+ * copies the result out.  Other shapes on the skinny kernel's TMA path (m <= 16, 512 <= K <= 32768)
+ * take two launches: the kernel stores fp16 results and raises a per-rank flag, a second small
+ * kernel waits for all flags and copies out.  All ranks must make the same sequence of calls;
+ * work that reads output_ptr must be enqueued on `stream` before the next gather call.  A shape
+ * outside both paths (row-wise blocks, block < 64, m > 16) is refused with an error text starting
+ * "Kernel execution failed: unsupported": compute with blkq4_fp16_gemm_sm80 and all-gather with
+ * the caller's collective instead.  blkq4_gather_status synchronises `stream` and returns 0, or
+ * (0x400 | rank) of the first rank whose data did not arrive in time; blkq4_gather_reset
+ * (device drained on every rank, between the same two calls on every rank) clears that state.
+ * blkq4_gather_destroy frees the rank's block: peers store into it from their own kernels, so
+ * every rank must have drained its stream, and a cross-rank barrier must have passed, before ANY
+ * rank destroys its context.
  */
 int blkq4_gather_create(int world, int rank, size_t max_out_bytes, void** ctx, void* ipc_handle_64_bytes,
                         void* error_message);
@@ -224,6 +235,7 @@ int blkq4_fp16_gemm_gather_sm100(
   unsigned flags,
   void* error_message);
 int blkq4_gather_status(void* ctx, void* stream);
+int blkq4_gather_reset(void* ctx);
 int blkq4_gather_destroy(void* ctx);
 
 /*
@@ -243,6 +255,14 @@ void blkq4_errmsg_destroy(void* errmsg);      /* delete                         
  * No counterpart in the reference, whose kernels have no such waits.
  */
 int blkq4_last_kernel_status(void* stream);
+
+/**
+ * Recovery after a non-zero blkq4_last_kernel_status: enqueues on `stream` the clearing of the
+ * kernels' status words and of the flag words of the library's static scratch array
+ * (blkq4_fp16_gemm_static_ws_sm100).  A caller-owned split-K workspace must be re-zeroed by its
+ * owner.  Allocates nothing.  No counterpart in the reference.
+ */
+int blkq4_reset(void* stream);
 
 /** Library identification: "gemmlib_b200 <version> sm_100a". */
 char const* blkq4_version(void);

@@ -33,9 +33,16 @@ def test_two_calls_in_a_row_match_the_workspace_entry_point(case):
     want = torch.empty(M, N, dtype=torch.float16, device="cuda")
     capi.gemm(block, True, M, N, K, a, pw, ps, pz, want, workspace=ws)          # the existing entry point
     outs = [torch.full((M, N), float("nan"), dtype=torch.float16, device="cuda") for _ in range(2)]
+    capi.gemm_static_ws(block, True, M, N, K, a, pw, ps, pz, outs[0])            # first call on this device: set-up
+    torch.cuda.synchronize()
+    # nothing is allocated by a call: neither through torch's allocator nor behind its back
+    free_before, _ = torch.cuda.mem_get_info()
+    torch_before = torch.cuda.memory_allocated()
     for o in outs:                                                               # two calls in a row
         capi.gemm_static_ws(block, True, M, N, K, a, pw, ps, pz, o)
     torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() == torch_before
+    assert torch.cuda.mem_get_info()[0] == free_before
     assert capi.last_kernel_status() == 0
     for o in outs:
         assert torch.equal(o.view(torch.int16), want.view(torch.int16))
@@ -63,4 +70,25 @@ def test_a_plan_beyond_the_scratch_is_refused():
     capi.gemm_static_ws(64, True, M2, N, K, a2, pw, ps, pz, o1)
     capi.gemm(64, True, M2, N, K, a2, pw, ps, pz, o2)
     torch.cuda.synchronize()
+    assert torch.equal(o1.view(torch.int16), o2.view(torch.int16))
+
+
+def test_reset_clears_the_scratch_flags_and_status_words():
+    """blkq4_reset: the recovery a caller runs after a non-zero kernel status.  Here nothing has
+    expired; the call must be harmless (enqueued on the stream, allocating nothing) and leave the
+    entry point working."""
+    from gemmlib_b200 import capi
+
+    block, has_zp, M, N, K = 64, True, 512, 1024, 2048
+    a, pw, ps, pz = _problem(block, has_zp, M, N, K)
+    o1 = torch.empty(M, N, dtype=torch.float16, device="cuda")
+    o2 = torch.empty_like(o1)
+    capi.gemm_static_ws(block, True, M, N, K, a, pw, ps, pz, o1)
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    capi.reset()
+    capi.gemm_static_ws(block, True, M, N, K, a, pw, ps, pz, o2)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert capi.last_kernel_status() == 0
     assert torch.equal(o1.view(torch.int16), o2.view(torch.int16))
