@@ -38,6 +38,11 @@ std::string launch_gemv_stream(int block, bool colwise, int M, int N, int K, cud
                                const uint8_t* zp, __half* out, const __half* bias, unsigned flags,
                                const GatherTable* gt = nullptr);
 
+// The same weight stream for 9 <= M <= 16 (two row groups, two tiles per pass, activations from L2).
+std::string launch_gemv_wide(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
+                             const __half* a, const uint8_t* packed, const __half* scales,
+                             const uint8_t* zp, __half* out, const __half* bias, unsigned flags);
+
 // Multiprocessor count of the CURRENT device (cached per device index).
 int sm_count();
 
@@ -78,6 +83,9 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
 // Bytes of zero-initialised workspace with which launch_gemm_tc would split K for this problem
 // (0: it would not).
 size_t gemm_tc_workspace_bytes(int M, int N, int K);
+// True when the preferred plan of the problem is the balanced one (more tiles than SMs): its workspace
+// only buys balance; without it the same kernel runs in whole rounds.
+bool gemm_tc_plan_balanced(int M, int N, int K);
 
 // Synchronises `stream` and returns the tensor-core kernel's device error word
 // (0 = every bounded wait completed; -1 = the stream itself reported an error).

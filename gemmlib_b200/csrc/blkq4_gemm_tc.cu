@@ -33,6 +33,7 @@
 // src/mickey/cutlass_ext/q4gemm/warp/quantb_meta_mma_tensor_op_tile_iterator.h:69-104, :436-543).
 #include <cstddef>
 #include <cstdint>
+#include <cstdlib>
 
 #include "blkq4_common.cuh"
 #include "blkq4_tma.cuh"
@@ -57,12 +58,18 @@ constexpr int kDeqStages = 8;     // dequantized weights in tensor memory
 // tcgen05.commit costs about as much pipe time as one 128x256x16 MMA (measured: 128 cycles per MMA
 // back to back, 241 with a commit after each), so completion is signalled once per kCommitSteps
 // k steps and both rings are released at that granularity.
-constexpr int kCommitSteps = 1;
+#ifndef BLKQ4_TC_COMMIT_STEPS
+#define BLKQ4_TC_COMMIT_STEPS 1
+#endif
+constexpr int kCommitSteps = BLKQ4_TC_COMMIT_STEPS;
 constexpr int kDoneBars = kDeqStages / kCommitSteps;
 static_assert(kActStages % kCommitSteps == 0 && kDeqStages % kCommitSteps == 0, "rings are released per commit group");
 constexpr int kDeqCols = BLOCK_K / 2;  // TMEM columns of one dequantized stage: 2 fp16 per column
-constexpr int kNumDeqWarps = 8;
-constexpr int kDeqGroups = 2;     // warp groups taking alternate k steps
+#ifndef BLKQ4_TC_DEQ_GROUPS
+#define BLKQ4_TC_DEQ_GROUPS 2
+#endif
+constexpr int kDeqGroups = BLKQ4_TC_DEQ_GROUPS;     // warp groups taking k steps in turn
+constexpr int kNumDeqWarps = 4 * kDeqGroups;
 constexpr int kWarpsPerDeqGroup = kNumDeqWarps / kDeqGroups;
 constexpr int kNumEpiWarps = 4;
 constexpr int kWeightProducerWarp = 2 + kNumEpiWarps + kNumDeqWarps;  // last warp
@@ -85,13 +92,22 @@ struct Params {
   uint32_t meta_row_bytes_s, meta_row_bytes_z;  // bytes per box row
   __half* out;
   const __half* bias;  // fp16 [N] added to the fp16 result, or null
-  // Split-K: a work item is (tile, part) with part < split covering k_per_item steps; parts
-  // 0 .. split-2 leave fp32 partial tiles in the workspace, the last part adds them to its own.
+  // Work items.  A tile's K range may be cut in parts that different CTAs compute: every part but
+  // one leaves an fp32 partial tile in the workspace, the remaining one adds them to its own.
+  //   balanced == 0: item = (tile, part), part < split covering k_per_item steps; CTA b takes items
+  //     b, b + grid, ...; the last part of a tile adds the others.
+  //   balanced == 1: the (tile, k step) sequence of the whole problem is cut in one contiguous range
+  //     per CTA (range_bound), so that every SM gets the same number of steps whatever the tile
+  //     count; a tile that straddles two ranges has its tail computed FIRST by the later CTA
+  //     (partial tile, slot = that CTA) and its head LAST by the earlier CTA, which adds the partial.
   int split_shift;     // log2(split), split in {1, 2, 4}
   int k_per_item;      // 64-k steps per work item
   int num_items;       // tiles << split_shift
-  float* ws_partials;  // [tile][split-1][BM][128] fp32
-  unsigned* ws_flags;  // [tile] arrivals (self-resetting)
+  int balanced;
+  int k_steps;         // K / 64
+  int total_steps;     // tiles * k_steps
+  float* ws_partials;  // balanced: [cta][BM][128] fp32; otherwise [tile][split-1][BM][128]
+  unsigned* ws_flags;  // balanced: [cta]; otherwise [tile]: arrivals (self-resetting)
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
@@ -184,6 +200,65 @@ __host__ __device__ inline uint32_t make_idesc_f16(int umma_m, int umma_n) {
   return (1u << 4) | ((uint32_t)(umma_n >> 3) << 17) | ((uint32_t)(umma_m >> 4) << 24);
 }
 
+// ---- work items -----------------------------------------------------------------------------
+
+constexpr int kMinPartSteps = 4;  // a range boundary closer than this to a tile boundary moves onto it
+
+// First step of CTA b's range in balanced mode (b == grid: the end of the last range).
+__host__ __device__ inline int range_bound(int total_steps, int k_steps, int grid, int b) {
+  int x = (int)((long long)b * total_steps / grid);
+  const int r = x % k_steps;
+  if (r < kMinPartSteps) x -= r;
+  else if (r > k_steps - kMinPartSteps) x += k_steps - r;
+  return x;
+}
+
+struct Item {
+  int tile, ks0, count;
+  int role;    // 0: whole tile; 1: writes its partial tile to `slot`; 2: adds `nparts` partial tiles from `slot` on
+  int slot, flag, nparts;
+};
+struct ItemCursor {
+  int pos, end;  // balanced: steps of the range still to do; otherwise: next item index, item count
+};
+__device__ __forceinline__ ItemCursor first_item(const Params& p) {
+  ItemCursor c;
+  if (p.balanced) {
+    c.pos = range_bound(p.total_steps, p.k_steps, (int)gridDim.x, (int)blockIdx.x);
+    c.end = range_bound(p.total_steps, p.k_steps, (int)gridDim.x, (int)blockIdx.x + 1);
+  } else {
+    c.pos = (int)blockIdx.x;
+    c.end = p.num_items;
+  }
+  return c;
+}
+__device__ __forceinline__ bool next_item(const Params& p, ItemCursor& c, Item& it) {
+  if (c.pos >= c.end) return false;
+  if (p.balanced) {
+    it.tile = c.pos / p.k_steps;
+    it.ks0 = c.pos - it.tile * p.k_steps;
+    it.count = min(p.k_steps - it.ks0, c.end - c.pos);
+    // a range is longer than a tile, so a cut tile has exactly two parts: its tail opens the later
+    // CTA's range, its head closes the earlier one's
+    it.role = it.ks0 > 0 ? 1 : (it.count < p.k_steps ? 2 : 0);
+    it.slot = it.flag = (int)blockIdx.x + (it.role == 2 ? 1 : 0);
+    it.nparts = 1;
+    c.pos += it.count;
+  } else {
+    const int split = 1 << p.split_shift;
+    it.tile = c.pos >> p.split_shift;
+    const int part = c.pos - (it.tile << p.split_shift);
+    it.ks0 = part * p.k_per_item;
+    it.count = p.k_per_item;
+    it.role = split == 1 ? 0 : (part < split - 1 ? 1 : 2);
+    it.slot = it.tile * (split - 1) + (it.role == 1 ? part : 0);
+    it.flag = it.tile;
+    it.nparts = split - 1;
+    c.pos += (int)gridDim.x;
+  }
+  return true;
+}
+
 // ---- shared-memory plan ---------------------------------------------------------------------
 
 struct SmemPlan {
@@ -274,11 +349,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     if (lane == 0) {
       asm volatile("griddepcontrol.wait;" ::: "memory");  // activations belong to stream order
       uint32_t it = 0;
-      for (int item = blockIdx.x; item < p.num_items; item += gridDim.x) {
-        const int tile = item >> p.split_shift;
-        const int m_tile = tile % p.m_tiles;
-        const int ks0 = (item - (tile << p.split_shift)) * p.k_per_item;
-        for (int ks = ks0; ks < ks0 + p.k_per_item; ++ks, ++it) {
+      ItemCursor cur = first_item(p);
+      Item item;
+      while (next_item(p, cur, item)) {
+        const int m_tile = item.tile % p.m_tiles;
+        for (int ks = item.ks0; ks < item.ks0 + item.count; ++ks, ++it) {
           const int sa = it % kActStages;
           if (it >= (uint32_t)kActStages) {
             const uint32_t g = (it - kActStages) / kCommitSteps;  // commit group of the stage's last user
@@ -298,11 +373,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       const uint32_t tx = kPackTileBytes + (uint32_t)p.meta_rows * p.meta_row_bytes_s +
                           (p.has_zp ? (uint32_t)p.meta_rows * p.meta_row_bytes_z : 0u);
       uint32_t it = 0;
-      for (int item = blockIdx.x; item < p.num_items; item += gridDim.x) {
-        const int tile = item >> p.split_shift;
-        const int n_tile = tile / p.m_tiles;
-        const int ks0 = (item - (tile << p.split_shift)) * p.k_per_item;
-        for (int ks = ks0; ks < ks0 + p.k_per_item; ++ks, ++it) {
+      ItemCursor cur = first_item(p);
+      Item item;
+      while (next_item(p, cur, item)) {
+        const int n_tile = item.tile / p.m_tiles;
+        for (int ks = item.ks0; ks < item.ks0 + item.count; ++ks, ++it) {
           const int s = it % kStages;
           if (it >= (uint32_t)kStages &&
               !mbar_wait(bar(BAR_PACK_FREE + s), ((it / kStages) - 1) & 1, abort_flag, 0x110 | s))
@@ -344,30 +419,53 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       const uint32_t a_tmem0 = tmem_base + (uint32_t)p.a_col0;
       uint32_t s = 0, sa = 0, par_s = 0, par_sa = 0, gdone = 0, it = 0, tcount = 0;
       uint32_t ab = 0, par_acc = 0;
-      for (int item = blockIdx.x; item < p.num_items; item += gridDim.x, ++tcount) {
-        if (tcount >= (uint32_t)p.acc_bufs &&
-            !mbar_wait(bar(BAR_ACC_EMPTY + ab), par_acc ^ 1u, abort_flag, 0x200 | ab))
-          goto mma_done;
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + ab * (uint32_t)p.BM;
-        for (int ks = 0; ks < p.k_per_item; ++ks, ++it) {
-          const uint32_t bar_a = bar(BAR_ACT_FULL) + 8u * sa, bar_d = bar(BAR_DEQ_FULL) + 8u * s;
-          if (!mbar_try_wait(bar_a, par_sa) && !mbar_wait(bar_a, par_sa, abort_flag, 0x210 | sa)) goto mma_done;
-          if (!mbar_try_wait(bar_d, par_s) && !mbar_wait(bar_d, par_s, abort_flag, 0x220 | s)) goto mma_done;
-          tc_fence_after();
-          // 16 k = 8 TMEM columns of the weights, 32 bytes (2 descriptor units) of the activation row
-          umma_f16_ts_x4(d_tmem, a_tmem0 + s * kDeqCols, act_lo0 + sa * act_lo_step, desc_hi, idesc,
-                         ks > 0 ? 1u : 0u);
-          if (it % kCommitSteps == kCommitSteps - 1) {
-            umma_commit(bar(BAR_MMA_DONE) + 8u * gdone);
-            if (++gdone == kDoneBars) gdone = 0;
-          }
-          if (++s == kDeqStages) { s = 0; par_s ^= 1u; }
-          if (++sa == kActStages) { sa = 0; par_sa ^= 1u; }
+      // The barriers of step i + 1 are polled (without blocking) BEFORE the MMAs of step i are
+      // issued, so that the poll's round trip to shared memory overlaps the issue instead of
+      // extending the dependent chain of the next step.
+      bool ready_a = false, ready_d = false;
+#define BLKQ4_TC_MMA_ITEM(COUNT)                                                                                    \
+  {                                                                                                                 \
+    if (tcount >= (uint32_t)p.acc_bufs &&                                                                           \
+        !mbar_wait(bar(BAR_ACC_EMPTY + ab), par_acc ^ 1u, abort_flag, 0x200 | ab))                                  \
+      goto mma_done;                                                                                                \
+    tc_fence_after();                                                                                               \
+    const uint32_t d_tmem = tmem_base + ab * (uint32_t)p.BM;                                                        \
+    for (int ks = 0; ks < (COUNT); ++ks, ++it) {                                                                    \
+      const uint32_t bar_a = bar(BAR_ACT_FULL) + 8u * sa, bar_d = bar(BAR_DEQ_FULL) + 8u * s;                       \
+      if (!ready_a && !mbar_try_wait(bar_a, par_sa) && !mbar_wait(bar_a, par_sa, abort_flag, 0x210 | sa))           \
+        goto mma_done;                                                                                              \
+      if (!ready_d && !mbar_try_wait(bar_d, par_s) && !mbar_wait(bar_d, par_s, abort_flag, 0x220 | s))              \
+        goto mma_done;                                                                                              \
+      tc_fence_after();                                                                                             \
+      /* 16 k = 8 TMEM columns of the weights, 32 bytes (2 descriptor units) of the activation row */              \
+      const uint32_t a_tmem = a_tmem0 + s * kDeqCols, b_lo = act_lo0 + sa * act_lo_step;                            \
+      if (++s == kDeqStages) { s = 0; par_s ^= 1u; }                                                                \
+      if (++sa == kActStages) { sa = 0; par_sa ^= 1u; }                                                             \
+      ready_a = mbar_test_wait(bar(BAR_ACT_FULL) + 8u * sa, par_sa);                                                \
+      ready_d = mbar_test_wait(bar(BAR_DEQ_FULL) + 8u * s, par_s);                                                  \
+      umma_f16_ts_x4(d_tmem, a_tmem, b_lo, desc_hi, idesc, ks > 0 ? 1u : 0u);                                       \
+      if (it % kCommitSteps == kCommitSteps - 1) {                                                                  \
+        umma_commit(bar(BAR_MMA_DONE) + 8u * gdone);                                                                \
+        if (++gdone == kDoneBars) gdone = 0;                                                                        \
+      }                                                                                                             \
+    }                                                                                                               \
+    umma_commit(bar(BAR_ACC_FULL + ab));                                                                            \
+    if (++ab == (uint32_t)p.acc_bufs) { ab = 0; par_acc ^= 1u; }                                                    \
+  }
+      if (!p.balanced) {
+        for (int item = blockIdx.x; item < p.num_items; item += gridDim.x, ++tcount) BLKQ4_TC_MMA_ITEM(p.k_per_item)
+      } else {
+        int pos = range_bound(p.total_steps, p.k_steps, (int)gridDim.x, (int)blockIdx.x);
+        const int end = range_bound(p.total_steps, p.k_steps, (int)gridDim.x, (int)blockIdx.x + 1);
+        int to_tile_end = p.k_steps - pos % p.k_steps;
+        for (; pos < end; ++tcount) {
+          const int count = min(to_tile_end, end - pos);
+          BLKQ4_TC_MMA_ITEM(count)
+          pos += count;
+          to_tile_end = p.k_steps;
         }
-        umma_commit(bar(BAR_ACC_FULL + ab));
-        if (++ab == (uint32_t)p.acc_bufs) { ab = 0; par_acc ^= 1u; }
       }
+#undef BLKQ4_TC_MMA_ITEM
     mma_done:;
     }
   } else if (warp < 2 + kNumEpiWarps) {
@@ -378,20 +476,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     const int quarter = warp & 3;
     uint32_t tcount = 0;
     asm volatile("griddepcontrol.wait;" ::: "memory");  // output and workspace belong to stream order
-    const int split = 1 << p.split_shift;
     const size_t tile_floats = (size_t)p.BM * TILE_N;
-    for (int item = blockIdx.x; item < p.num_items; item += gridDim.x, ++tcount) {
-      const int tile = item >> p.split_shift, part = item - (tile << p.split_shift);
-      const int n_tile = tile / p.m_tiles, m_tile = tile % p.m_tiles;
+    ItemCursor cur = first_item(p);
+    Item item;
+    for (; next_item(p, cur, item); ++tcount) {
+      const int n_tile = item.tile / p.m_tiles, m_tile = item.tile % p.m_tiles;
       const int ab = tcount % p.acc_bufs;
       if (!mbar_wait(bar(BAR_ACC_FULL + ab), (tcount / p.acc_bufs) & 1, abort_flag, 0x300 | ab)) break;
       tc_fence_after();
       const int n_l = quarter * 32 + lane;
-      if (part < split - 1) {
-        // ---- split-K, not the last part: fp32 partial tile [m][n] to the workspace: for a row m
+      if (item.role == 1) {
+        // ---- a part that hands over: fp32 partial tile [m][n] to the workspace: for a row m
         //      the 32 lanes of a warp write 128 contiguous bytes.  (One line per lane, [n][m] with
         //      16-byte accesses, was measured slower: 32 lines touched per instruction.)
-        float* dst_ws = p.ws_partials + ((size_t)tile * (split - 1) + part) * tile_floats + n_l;
+        float* dst_ws = p.ws_partials + (size_t)item.slot * tile_floats + n_l;
         const int rows = min(p.BM, p.M - m_tile * p.BM);
         for (int c0 = 0; c0 < rows; c0 += 32) {
           uint32_t r[32];
@@ -406,16 +504,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         __syncwarp();
         if (lane == 0) {
           mbar_arrive(bar(BAR_ACC_EMPTY + ab));
-          atomicAdd(p.ws_flags + tile, 1u);
+          atomicAdd(p.ws_flags + item.flag, 1u);
         }
         continue;
       }
-      if (split > 1) {
-        // ---- split-K, last part: wait (bounded) for the other parts' partial tiles ----
+      if (item.role == 2) {
+        // ---- the part that finishes the tile: wait (bounded) for the other parts' partial tiles ----
         if (lane == 0) {
-          const unsigned want = (unsigned)((split - 1) * kNumEpiWarps);
+          const unsigned want = (unsigned)(item.nparts * kNumEpiWarps);
           const long long t0 = clock64();
-          while (*reinterpret_cast<volatile unsigned*>(p.ws_flags + tile) < want) {
+          while (*reinterpret_cast<volatile unsigned*>(p.ws_flags + item.flag) < want) {
             if (*abort_flag || clock64() - t0 > kWaitCycles) {
               *abort_flag = 1;
               atomicCAS(&g_gemm_tc_error, 0, 0x320 | quarter);
@@ -427,7 +525,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         __syncwarp();
         if (*abort_flag) break;
       }
-      const float* src_ws = p.ws_partials + (size_t)tile * (split - 1) * tile_floats + n_l;
+      const float* src_ws = p.ws_partials + (size_t)item.slot * tile_floats + n_l;
       const int n = n_tile * TILE_N + quarter * 32 + lane;
       const int m0 = m_tile * p.BM;
       // Lanes pair up (n even / odd) so that every store carries two adjacent n (4 bytes per
@@ -440,9 +538,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(ab * p.BM + c0), r);
         tmem_ld_wait();
-        if (split > 1) {
+        if (item.role == 2) {
           // add the other parts in part order (a fixed order: the result is reproducible)
-          for (int q = 0; q < split - 1; ++q) {
+          for (int q = 0; q < item.nparts; ++q) {
             const float* sq = src_ws + (size_t)q * tile_floats + (size_t)c0 * TILE_N;
             float f[32];
 #pragma unroll
@@ -475,7 +573,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       if (lane == 0) {
         mbar_arrive(bar(BAR_ACC_EMPTY + ab));
         // the warp that completes the tile's count puts the flag back to zero for the next launch
-        if (split > 1 && atomicAdd(p.ws_flags + tile, 1u) == (unsigned)(split * kNumEpiWarps - 1)) p.ws_flags[tile] = 0u;
+        if (item.role == 2 && atomicAdd(p.ws_flags + item.flag, 1u) == (unsigned)((item.nparts + 1) * kNumEpiWarps - 1))
+          p.ws_flags[item.flag] = 0u;
       }
     }
   } else if (warp < kWeightProducerWarp) {
@@ -494,9 +593,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     const int np_l = 8 * (n_l >> 4) + (n_l & 7);
     const uint32_t nib_shift = (n_l & 8) ? 8u : 0u;
     const uint32_t tmem_row = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)p.a_col0;
-    int my_items = 0;
-    for (int item = blockIdx.x; item < p.num_items; item += gridDim.x) ++my_items;
-    const uint32_t total_its = (uint32_t)my_items * (uint32_t)p.k_per_item;
+    uint32_t total_its = 0;
+    {
+      ItemCursor cur = first_item(p);
+      Item item;
+      while (next_item(p, cur, item)) total_its += (uint32_t)item.count;
+    }
     for (uint32_t it = group; it < total_its; it += kDeqGroups) {
       const int s = it % kStages, d = it % kDeqStages;
       if (it >= (uint32_t)kDeqStages) {
@@ -591,11 +693,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
 
 namespace {
 
-// Split-K plan.  The kernel is persistent with one CTA per SM, so a problem with few output
-// tiles (prefill of a 4096-wide layer at M = 512: 64 tiles on 148 SMs) leaves SMs idle; cutting
-// every tile's K range in `split` work items fills them.
+// Work plan.  The kernel is persistent with one CTA per SM.  A problem with few output tiles
+// (prefill of a 4096-wide layer at M = 512: 64 tiles on 148 SMs) leaves SMs idle: cutting every
+// tile's K range in `split` work items fills them.  A problem with more tiles than SMs but not a
+// whole number of rounds (256 tiles: the second round keeps 108 of 148 SMs busy) is cut in one
+// contiguous range of k steps per CTA instead ("balanced", see Params).
 struct SplitPlan {
   int split_shift;
+  int balanced;
   size_t flags_bytes, total_bytes;  // workspace: [flags, 256-byte aligned][partials]
 };
 
@@ -604,7 +709,24 @@ SplitPlan plan_split(int M, int N, int K, size_t ws_bytes_available) {
   const int tiles = ((M + BM - 1) / BM) * ((N + TILE_N - 1) / TILE_N);
   const int k_steps = K / BLOCK_K;
   const int sms = sm_count() > 0 ? sm_count() : 148;
-  SplitPlan best{0, 0, 0};
+  SplitPlan best{0, 0, 0, 0};
+  if (tiles > sms) {
+    // balanced ranges: every range longer than a tile (a cut tile then has exactly two parts), and
+    // only when whole rounds would leave more than a fifth of the SM time idle.  Measured on B200:
+    // 224 tiles of K = 8192 at M = 64: 98 -> 83 us; 172 tiles (M = 512, 4096 -> 11008): 55 -> 49 us;
+    // 256 tiles (M = 2048, N = K = 4096; 86 % busy in whole rounds): 62 -> 66 us, the extra work item
+    // and the fp32 exchange cost more than the balance gains, hence the threshold.
+    const int rounds = (tiles + sms - 1) / sms;
+    const long long total_steps = (long long)tiles * k_steps;
+    static const bool off = getenv("BLKQ4_TC_NO_BALANCE") != nullptr;
+    if (!off && total_steps < (1ll << 30) / sms && total_steps / sms >= k_steps + 2 * kMinPartSteps &&
+        (double)tiles < 0.80 * rounds * sms) {
+      const size_t flags = ((size_t)sms * sizeof(unsigned) + 255) & ~(size_t)255;
+      const size_t total = flags + (size_t)sms * BM * TILE_N * sizeof(float);
+      if (total <= ws_bytes_available) best = SplitPlan{0, 1, flags, total};
+    }
+    return best;
+  }
   // Split only when every work item still gets an SM of its own (one round): measured on B200 a
   // second round of half-size items loses more to the fp32 exchange than it gains in balance.
   for (int shift = 1; shift <= 2; ++shift) {
@@ -613,7 +735,7 @@ SplitPlan plan_split(int M, int N, int K, size_t ws_bytes_available) {
     const size_t flags = ((size_t)tiles * sizeof(unsigned) + 255) & ~(size_t)255;
     const size_t total = flags + (size_t)tiles * (split - 1) * BM * TILE_N * sizeof(float);
     if (total > ws_bytes_available) continue;
-    best = SplitPlan{shift, flags, total};
+    best = SplitPlan{shift, 0, flags, total};
   }
   return best;
 }
@@ -623,6 +745,10 @@ SplitPlan plan_split(int M, int N, int K, size_t ws_bytes_available) {
 size_t gemm_tc_workspace_bytes(int M, int N, int K) {
   if (M <= 16) return 0;
   return plan_split(M, N, K, ~(size_t)0).total_bytes;
+}
+
+bool gemm_tc_plan_balanced(int M, int N, int K) {
+  return M > 16 && plan_split(M, N, K, ~(size_t)0).balanced != 0;
 }
 
 std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
@@ -678,10 +804,13 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
   const int sms = sm_count();
   const int num_tiles = p.m_tiles * p.n_tiles;
   const SplitPlan sp = (workspace && reinterpret_cast<uintptr_t>(workspace) % 256 == 0)
-                           ? plan_split(M, N, K, workspace_bytes) : SplitPlan{0, 0, 0};
+                           ? plan_split(M, N, K, workspace_bytes) : SplitPlan{0, 0, 0, 0};
   p.split_shift = sp.split_shift;
   p.k_per_item = (K / BLOCK_K) >> sp.split_shift;
   p.num_items = num_tiles << sp.split_shift;
+  p.balanced = sp.balanced;
+  p.k_steps = K / BLOCK_K;
+  p.total_steps = sp.balanced ? num_tiles * p.k_steps : 0;
   p.ws_flags = reinterpret_cast<unsigned*>(workspace);
   p.ws_partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + sp.flags_bytes);
   const int grid = p.num_items < sms ? p.num_items : sms;

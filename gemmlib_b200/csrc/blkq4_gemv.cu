@@ -796,7 +796,8 @@ std::string launch_gemv(int block, bool colwise, int M, int N, int K, cudaStream
   static const int env_generic = env_int("BLKQ4_GEMV_GENERIC"), env_no_stream = env_int("BLKQ4_GEMV_NO_STREAM");
   // Decode shapes first: the cp.async stream kernel (blkq4_gemv_stream.cu).
   if (!env_generic && !env_no_stream) {
-    const std::string r = launch_gemv_stream(block, colwise, M, N, K, stream, a, packed, scales, zp, out, bias, flags);
+    const std::string r = M <= 8 ? launch_gemv_stream(block, colwise, M, N, K, stream, a, packed, scales, zp, out, bias, flags)
+                                 : launch_gemv_wide(block, colwise, M, N, K, stream, a, packed, scales, zp, out, bias, flags);
     if (r != kStreamUnsupported) return r;
   }
   // Fast path: one scale per 64-k step; at least one 512-k unit (the last one may be partial), meta

@@ -36,18 +36,14 @@
 #include <string>
 
 #include "blkq4_common.cuh"
+#include "blkq4_stream.cuh"
 #include "blkq4_tma.cuh"
 #include "ms_blkq4gemm.h"
 
 namespace blkq4 {
 namespace {
 
-constexpr int kWarps = 8;            // warps per CTA = K splits
-constexpr int kGroupSteps = 4;       // 64-k steps per group (one ring slot)
-constexpr int kSlotW = kGroupSteps * 512;   // [step][lane] 16 bytes
-constexpr int kSlotS = kGroupSteps * 32;    // [step][16] fp16
-constexpr int kSlotZ = kGroupSteps * 16;    // [step][16] u8
-constexpr int kSlotBytes = kSlotW + kSlotS + kSlotZ;  // 2240
+using namespace stream;
 constexpr int kCorrStep = 4 * 16;    // bytes of mma-initialising terms per step: four row pairs, float4 each
 
 struct StreamParams {
@@ -66,82 +62,6 @@ struct StreamParams {
 };
 
 constexpr long long kGatherWaitCycles = 2000000000ll;  // ~1 s
-
-__device__ __forceinline__ uint2 ld_relaxed_sys_v2(const void* p) {
-  uint2 v;
-  asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_relaxed_sys_v2(void* p, uint32_t x, uint32_t y) {
-  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(x), "r"(y) : "memory");
-}
-
-__device__ __forceinline__ uint32_t lop3_and_or(uint32_t x, uint32_t mask, uint32_t bits) {
-  uint32_t d;
-  asm("lop3.b32 %0, %1, %2, %3, 0xea;" : "=r"(d) : "r"(x), "r"(mask), "r"(bits));  // (x & mask) | bits
-  return d;
-}
-// D = A x B + C with C in its own four registers (the negated activation-only terms).
-__device__ __forceinline__ void mma_init(float d[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1, const float4& c) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
-      "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
-      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c.x), "f"(c.y), "f"(c.z), "f"(c.w));
-}
-__device__ __forceinline__ void mma_acc(float d[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                        uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
-      "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-// Shared-memory loads with the offset as an immediate: no address arithmetic per access.
-template <int OFF>
-__device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr), "n"(OFF));
-  return v;
-}
-template <int OFF>
-__device__ __forceinline__ float4 lds_f4(uint32_t addr) {
-  float4 v;
-  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4+%5];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr), "n"(OFF));
-  return v;
-}
-__device__ __forceinline__ float2 lds_f2(uint32_t addr) {
-  float2 v;
-  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
-  return v;
-}
-template <int OFF>
-__device__ __forceinline__ float lds_half_as_float(uint32_t addr) {
-  float v;
-  asm volatile("{\n\t.reg .b16 h;\n\tld.shared.b16 h, [%1+%2];\n\tcvt.f32.f16 %0, h;\n\t}" : "=f"(v) : "r"(addr), "n"(OFF));
-  return v;
-}
-__device__ __forceinline__ float lds_u8_as_float(uint32_t addr) {
-  float v;
-  asm volatile("{\n\t.reg .b32 r;\n\tld.shared.u8 r, [%1];\n\tcvt.rn.f32.u32 %0, r;\n\t}" : "=f"(v) : "r"(addr));
-  return v;
-}
-// 16-byte global -> shared copy (L2 only), executed where pred != 0.  OFF bytes into the global row
-// is 8 * OFF bytes into the slot (64 bytes of a packed column per step, 512 bytes of slot per step).
-template <int OFF>
-__device__ __forceinline__ void cp_async16_if(uint32_t dst, const void* src, uint32_t pred) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %2, 0;\n\t"
-      "@p cp.async.cg.shared.global.L2::128B [%0+%3], [%1+%4], 16;\n\t}"
-      ::"r"(dst), "l"(src), "r"(pred), "n"(OFF * 8), "n"(OFF)
-      : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // Shared memory: rings [kWarps][D][kSlotBytes] | s_corr [steps][4] float4 | s_asum [steps][8] (zero points)
 //                | s_part [2][PW][16][MS] | s_stage [8][16] fp16 (gather) | s_a [M][a_pitch]
@@ -254,33 +174,48 @@ gemv_stream_kernel(const StreamParams p) {
   {
     const int slice_k0 = gb * (GS * 64);
     const int chunks = myg * (GS * 8);  // a multiple of 32
-    for (int m = 0; m < M; ++m) {
+    auto finish_row = [&](int m, int k0, const uint4& v) {
+      *reinterpret_cast<uint4*>(s_a + (size_t)m * p.a_pitch + k0) = v;
+      const __half2* h = reinterpret_cast<const __half2*>(&v);
+      float s = 0.0f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(h[e]);
+        s += f.x + f.y;
+      }
+      // the eight lanes of a step: sum the four chunks of equal parity, then pair lo with hi
+      s += __shfl_xor_sync(0xffffffffu, s, 2);
+      s += __shfl_xor_sync(0xffffffffu, s, 4);
+      const float other = __shfl_xor_sync(0xffffffffu, s, 1);
+      if ((lane & 7) == 0) {
+        const float lo = s, hi = other;
+        const int step = k0 >> 6;
+        // one float4 per row pair (m even, m odd, m even, m odd): the accumulator rows n and n + 8 start alike
+        float* dst = s_corr + ((size_t)step * 4 + (m >> 1)) * 4 + (m & 1);
+        const float nb = -(1024.0f * lo + 64.0f * hi);
+        const float c = HAS_ZP ? nb : nb - 8.0f * (lo + hi);
+        dst[0] = c;
+        dst[2] = c;
+        if (HAS_ZP) s_asum[(size_t)step * 8 + m] = lo + hi;
+      }
+    };
+    if (MZ == 2) {
+      for (int m = 0; m < M; ++m)
+        for (int c0 = 0; c0 < chunks; c0 += 32) {
+          const int k0 = slice_k0 + (c0 + lane) * 8;
+          finish_row(m, k0, __ldg(reinterpret_cast<const uint4*>(p.a + (size_t)m * K + k0)));
+        }
+    } else {
+      // several rows: all rows' loads of a chunk first (one L2 round trip per chunk, not one per row)
       for (int c0 = 0; c0 < chunks; c0 += 32) {
         const int k0 = slice_k0 + (c0 + lane) * 8;
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.a + (size_t)m * K + k0));
-        *reinterpret_cast<uint4*>(s_a + (size_t)m * p.a_pitch + k0) = v;
-        const __half2* h = reinterpret_cast<const __half2*>(&v);
-        float s = 0.0f;
+        uint4 v[8];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = __half22float2(h[e]);
-          s += f.x + f.y;
-        }
-        // the eight lanes of a step: sum the four chunks of equal parity, then pair lo with hi
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        s += __shfl_xor_sync(0xffffffffu, s, 4);
-        const float other = __shfl_xor_sync(0xffffffffu, s, 1);
-        if ((lane & 7) == 0) {
-          const float lo = s, hi = other;
-          const int step = k0 >> 6;
-          // one float4 per row pair (m even, m odd, m even, m odd): the accumulator rows n and n + 8 start alike
-          float* dst = s_corr + ((size_t)step * 4 + (m >> 1)) * 4 + (m & 1);
-          const float nb = -(1024.0f * lo + 64.0f * hi);
-          const float c = HAS_ZP ? nb : nb - 8.0f * (lo + hi);
-          dst[0] = c;
-          dst[2] = c;
-          if (HAS_ZP) s_asum[(size_t)step * 8 + m] = lo + hi;
-        }
+        for (int m = 0; m < 8; ++m)
+          if (m < M) v[m] = __ldg(reinterpret_cast<const uint4*>(p.a + (size_t)m * K + k0));
+#pragma unroll
+        for (int m = 0; m < 8; ++m)
+          if (m < M) finish_row(m, k0, v[m]);
       }
     }
   }
@@ -528,8 +463,8 @@ std::string launch_gemv_stream(int block, bool colwise, int M, int N, int K, cud
     if (D == 4) return small_m ? launch_T<true, 4, 2, G>(p, smem, grid, stream, early) : launch_T<true, 4, 8, G>(p, smem, grid, stream, early); \
     return small_m ? launch_T<true, 2, 2, G>(p, smem, grid, stream, early) : launch_T<true, 2, 8, G>(p, smem, grid, stream, early); \
   }                                                                                                                  \
-  if (D == 4) return launch_T<false, 4, 2, G>(p, smem, grid, stream, early);                                         \
-  return launch_T<false, 2, 2, G>(p, smem, grid, stream, early);
+  if (D == 4) return small_m ? launch_T<false, 4, 2, G>(p, smem, grid, stream, early) : launch_T<false, 4, 8, G>(p, smem, grid, stream, early); \
+  return small_m ? launch_T<false, 2, 2, G>(p, smem, grid, stream, early) : launch_T<false, 2, 8, G>(p, smem, grid, stream, early);
   if (gt) { BLKQ4_STREAM_LAUNCH(true) }
   BLKQ4_STREAM_LAUNCH(false)
 #undef BLKQ4_STREAM_LAUNCH

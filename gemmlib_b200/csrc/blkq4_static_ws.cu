@@ -9,6 +9,7 @@
 
 #include <cuda_runtime.h>
 
+#include "blkq4_common.cuh"
 #include "ms_blkq4gemm.h"
 
 namespace {
@@ -75,7 +76,9 @@ extern "C" int blkq4_fp16_gemm_static_ws_sm100(int block_size, bool column_wise_
                                                size_t output_size, void const* bias_ptr, size_t bias_size,
                                                unsigned flags, void* err) {
   const size_t need = blkq4_gemm_workspace_size(m, n, k);
-  if (need > kStaticScratchBytes)
+  // A balanced plan (more tiles than SMs) that does not fit simply runs in whole rounds, as it would
+  // with no workspace; a split-K plan that does not fit is refused.
+  if (need > kStaticScratchBytes && !blkq4::gemm_tc_plan_balanced(m, n, k))
     return fail(err, "Split-K workspace of " + std::to_string(need) + " bytes exceeds the static scratch of " +
                          std::to_string(kStaticScratchBytes) + " bytes");
   std::string why;

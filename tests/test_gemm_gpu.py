@@ -196,13 +196,45 @@ def test_split_k_with_workspace(case):
     assert (bits(r3) == bits(plain)).all()
 
 
-def test_split_k_is_not_planned_for_full_grids():
+@pytest.mark.parametrize("case", [(64, True, True, 48, 28672, 1024), (128, True, False, 300, 11008, 4096),
+                                  (32, False, True, 100, 22528, 4096)],
+                         ids=lambda c: "-".join(map(str, c)))
+def test_balanced_ranges_with_workspace(case):
+    """More output tiles than SMs, but far from a whole number of rounds: with a workspace every CTA
+    takes one contiguous range of k steps and a tile cut by a range boundary is finished through an
+    fp32 partial tile.  Same parity bars; flag words back to zero; runs agree bit for bit; without
+    the workspace the kernel runs in whole rounds."""
     from gemmlib_b200 import capi
 
-    assert capi.gemm_workspace_size(2048, 4096, 4096) == 0   # 256 tiles on 148 SMs: nothing idle
-    assert capi.gemm_workspace_size(512, 11008, 4096) == 0   # 172 tiles: a second round would cost more
+    block, colwise, has_zp, M, N, K = case
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    tiles = -(-M // min(256, -(-M // 16) * 16)) * -(-N // 128)
+    if not (tiles > sms and tiles < 0.8 * -(-tiles // sms) * sms and tiles * (K // 64) // sms >= K // 64 + 8):
+        pytest.skip(f"{tiles} tiles on {sms} SMs: not a balanced plan on this device")
+    need = capi.gemm_workspace_size(M, N, K)
+    assert need > 4 * sms
+    ws = torch.zeros(need, dtype=torch.uint8, device="cuda")
+    check_gaussian(block, colwise, has_zp, M, N, K, workspace=ws)
+    assert int(ws[: 4 * sms].view(torch.int32).abs().sum()) == 0
+    w = gaussian_weight(N, K, seed=K + N)
+    a = gaussian_act(M, K, seed=M).numpy()
+    pw, ps, pz = O.quant_prepack(block, colwise, w.numpy(), has_zp)
+    r1 = gpu_gemm(block, colwise, a, N, pw, ps, pz, workspace=ws)
+    r2 = gpu_gemm(block, colwise, a, N, pw, ps, pz, workspace=ws)
+    assert (bits(r1) == bits(r2)).all()
+    assert capi.last_kernel_status() == 0
+    # whole rounds (no workspace) sum every tile in one accumulator: equal up to fp32 summation order
+    plain = gpu_gemm(block, colwise, a, N, pw, ps, pz)
+    assert np.abs(r1.astype(np.float32) - plain.astype(np.float32)).max() <= 2e-3 * max(1.0, float(np.abs(plain).max()))
+
+
+def test_workspace_plans():
+    from gemmlib_b200 import capi
+
+    assert capi.gemm_workspace_size(2048, 4096, 4096) == 0   # 256 tiles on 148 SMs: 86 % busy, left alone
     assert capi.gemm_workspace_size(16, 4096, 4096) == 0     # skinny kernel
-    assert capi.gemm_workspace_size(512, 4096, 4096) > 0
+    assert capi.gemm_workspace_size(512, 4096, 4096) > 0     # 64 tiles: split-K
+    assert capi.gemm_workspace_size(512, 11008, 4096) > 0    # 172 tiles: balanced ranges
 
 
 def test_config_c1_cpu_reference_case():
