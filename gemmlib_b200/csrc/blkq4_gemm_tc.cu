@@ -36,6 +36,7 @@
 #include <cstdlib>
 
 #include "blkq4_common.cuh"
+#include "blkq4_tc.cuh"
 #include "blkq4_tma.cuh"
 #include "ms_blkq4gemm.h"
 
@@ -45,38 +46,28 @@ __device__ int g_gemm_tc_error = 0;  // 0 ok; otherwise (role << 8) | barrier id
 
 namespace {
 
-constexpr int TILE_N = 128;       // weight columns per tile (UMMA M)
-constexpr int BLOCK_K = 64;       // k per pipeline step: one 128-byte swizzle row of fp16
-constexpr int UMMA_K = 16;
+using namespace tc;
 // Two rings.  The weight path (TMA -> shared memory -> dequantize -> tensor memory -> MMA) has a
 // loop latency of several step times, so it is eight stages deep; its stages are small (5.5 KB of
 // shared memory, 32 TMEM columns).  The activation path (TMA -> shared memory -> MMA) is short
 // but its stages are 32 KB, so it gets six.
 constexpr int kActStages = 6;
-constexpr int kStages = 6;        // weight ring in shared memory: packed tile + scales + zero points
+// The weight ring in shared memory (packed tile + scales + zero points per stage) is a template
+// parameter of the kernels.
+constexpr int kPairWeightStages = 16;
 constexpr int kDeqStages = 8;     // dequantized weights in tensor memory
 // tcgen05.commit costs about as much pipe time as one 128x256x16 MMA (measured: 128 cycles per MMA
 // back to back, 241 with a commit after each), so completion is signalled once per kCommitSteps
 // k steps and both rings are released at that granularity.
-#ifndef BLKQ4_TC_COMMIT_STEPS
-#define BLKQ4_TC_COMMIT_STEPS 1
-#endif
-constexpr int kCommitSteps = BLKQ4_TC_COMMIT_STEPS;
+constexpr int kCommitSteps = 1;
 constexpr int kDoneBars = kDeqStages / kCommitSteps;
 static_assert(kActStages % kCommitSteps == 0 && kDeqStages % kCommitSteps == 0, "rings are released per commit group");
-constexpr int kDeqCols = BLOCK_K / 2;  // TMEM columns of one dequantized stage: 2 fp16 per column
-#ifndef BLKQ4_TC_DEQ_GROUPS
-#define BLKQ4_TC_DEQ_GROUPS 2
-#endif
-constexpr int kDeqGroups = BLKQ4_TC_DEQ_GROUPS;     // warp groups taking k steps in turn
+constexpr int kDeqGroups = 2;     // warp groups taking k steps in turn
 constexpr int kNumDeqWarps = 4 * kDeqGroups;
 constexpr int kWarpsPerDeqGroup = kNumDeqWarps / kDeqGroups;
 constexpr int kNumEpiWarps = 4;
 constexpr int kWeightProducerWarp = 2 + kNumEpiWarps + kNumDeqWarps;  // last warp
 constexpr int kThreads = 32 * (3 + kNumEpiWarps + kNumDeqWarps);
-constexpr int kPackTileBytes = (TILE_N / 2) * BLOCK_K;  // 4 KB: 64 packed columns x 64 bytes
-constexpr int kScaleTileBytes = 1024;
-constexpr int kZpTileBytes = 512;
 constexpr long long kWaitCycles = 4000000000ll;  // ~2 s: far beyond any legitimate wait
 
 struct Params {
@@ -116,90 +107,6 @@ struct Params {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int who) {
   return mbar_wait_bounded(bar, parity, abort_flag, &g_gemm_tc_error, who, kWaitCycles);
 }
-__device__ __forceinline__ void tc_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-// First operand from tensor memory: 128 lanes (rows) x 8 columns per 16 k, two fp16 per column.
-__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
-                                            uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// The four MMAs of one 64-k step: operand A advances 8 TMEM columns, operand B two
-// descriptor units (32 bytes) per 16 k.  Only the first may overwrite the accumulator.
-__device__ __forceinline__ void umma_f16_ts_x4(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
-                                               uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t.reg .b64 b0, b1, b2, b3;\n\t.reg .b32 l1, l2, l3, a1, a2, a3;\n\t"
-      "setp.ne.b32 p, %5, 0;\n\t"
-      "setp.eq.b32 q, 0, 0;\n\t"
-      "add.u32 l1, %2, 2;\n\tadd.u32 l2, %2, 4;\n\tadd.u32 l3, %2, 6;\n\t"
-      "add.u32 a1, %1, 8;\n\tadd.u32 a2, %1, 16;\n\tadd.u32 a3, %1, 24;\n\t"
-      "mov.b64 b0, {%2, %3};\n\tmov.b64 b1, {l1, %3};\n\tmov.b64 b2, {l2, %3};\n\tmov.b64 b3, {l3, %3};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], b0, %4, p;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], b1, %4, q;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], b2, %4, q;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], b3, %4, q;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() {
-  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() {
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major operand tile stored as rows of 128 bytes
-// (64 fp16) with the 128-byte swizzle, rows contiguous, tile base 1024-byte aligned:
-// start address >> 4 in bits 0-13, leading byte offset (unused for swizzled K-major) = 1
-// in bits 16-29, stride byte offset 1024 >> 4 (one 8-row group) in bits 32-45, descriptor
-// version 1 in bits 46-47, layout type 2 (SWIZZLE_128B) in bits 61-63.
-__device__ __forceinline__ uint64_t make_sw128_kmajor_desc(uint32_t smem_addr) {
-  return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) |
-         (2ull << 61);
-}
-// Instruction descriptor, kind::f16: fp32 accumulator (bits 4-5 = 1), fp16 A and B
-// (formats 0), both K-major, N >> 3 in bits 17-22, M >> 4 in bits 24-28.
-__host__ __device__ inline uint32_t make_idesc_f16(int umma_m, int umma_n) {
-  return (1u << 4) | ((uint32_t)(umma_n >> 3) << 17) | ((uint32_t)(umma_m >> 4) << 24);
-}
-
 // ---- work items -----------------------------------------------------------------------------
 
 constexpr int kMinPartSteps = 4;  // a range boundary closer than this to a tile boundary moves onto it
@@ -265,7 +172,7 @@ struct SmemPlan {
   uint32_t act, pack, scale, zp, bars, total;
   uint32_t act_bytes;
 };
-__host__ __device__ inline SmemPlan make_plan(int BM) {
+__host__ __device__ inline SmemPlan make_plan(int BM, int kStages) {
   SmemPlan p;
   p.act_bytes = (uint32_t)BM * 128u;
   uint32_t o = 0;
@@ -280,27 +187,28 @@ __host__ __device__ inline SmemPlan make_plan(int BM) {
 
 // Barrier slots (8 bytes each) inside the barrier block.  Stage s of the TMA ring and stage s
 // of the dequantized ring belong to the same k step, so one "MMA done" barrier frees both.
-enum : int {
-  BAR_ACT_FULL = 0,                       // [kActStages] activation tile landed (-> MMA issuer)
-  BAR_FULL = BAR_ACT_FULL + kActStages,   // [kStages] packed weights + meta landed (-> dequantizers)
-  BAR_PACK_FREE = BAR_FULL + kStages,     // [kStages] packed weights / meta read (dequantizers -> producer)
-  BAR_DEQ_FULL = BAR_PACK_FREE + kStages, // [kDeqStages] dequantized stage written to TMEM (-> MMA issuer)
-  BAR_MMA_DONE = BAR_DEQ_FULL + kDeqStages,  // [kDoneBars] MMAs of commit group g = it / kCommitSteps retired, index g % kDoneBars
-  BAR_ACC_FULL = BAR_MMA_DONE + kDoneBars,  // [2] accumulator complete
-  BAR_ACC_EMPTY = BAR_ACC_FULL + 2,       // [2] accumulator drained by the epilogue
-  BAR_COUNT = BAR_ACC_EMPTY + 2
-};
-static_assert(BAR_COUNT * 8 + 16 <= 512, "barrier block too small");
+#define BLKQ4_TC_BARRIER_SLOTS(WS)                                                                                 \
+  constexpr int kStages = (WS);                                                                                    \
+  constexpr int BAR_ACT_FULL = 0;                        /* [kActStages] activation tile landed (-> MMA issuer) */  \
+  constexpr int BAR_FULL = BAR_ACT_FULL + kActStages;    /* [kStages] packed weights + meta landed (-> dequantizers) */ \
+  constexpr int BAR_PACK_FREE = BAR_FULL + kStages;      /* [kStages] packed weights / meta read (-> producer) */   \
+  constexpr int BAR_DEQ_FULL = BAR_PACK_FREE + kStages;  /* [kDeqStages] dequantized stage in TMEM (-> MMA issuer) */ \
+  constexpr int BAR_MMA_DONE = BAR_DEQ_FULL + kDeqStages;  /* [kDoneBars] commit group g = it / kCommitSteps retired, index g % kDoneBars */ \
+  constexpr int BAR_ACC_FULL = BAR_MMA_DONE + kDoneBars; /* [2] accumulator complete */                             \
+  constexpr int BAR_ACC_EMPTY = BAR_ACC_FULL + 2;        /* [2] accumulator drained by the epilogue */              \
+  constexpr int BAR_COUNT = BAR_ACC_EMPTY + 2;                                                                      \
+  static_assert(BAR_COUNT * 8 + 16 <= 512, "barrier block too small");
 
-template <bool COLWISE>
+template <bool COLWISE, int WS>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_pack,
                const __grid_constant__ CUtensorMap tm_scale, const __grid_constant__ CUtensorMap tm_zp,
                const Params p) {
+  BLKQ4_TC_BARRIER_SLOTS(WS)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const SmemPlan plan = make_plan(p.BM);
+  const SmemPlan plan = make_plan(p.BM, kStages);
   const uint32_t act_stride = (plan.act_bytes + 1023u) & ~1023u;
   const uint32_t bars = base + plan.bars;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + plan.bars + BAR_COUNT * 8);
@@ -611,59 +519,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       const uint8_t* sc_tile = base_ptr + plan.scale + s * kScaleTileBytes;
       const uint8_t* zp_tile = base_ptr + plan.zp + s * kZpTileBytes;
       uint32_t out[32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {  // 16-byte chunk: k in [16 c, 16 c + 16)
-        const uint4 wv = *reinterpret_cast<const uint4*>(pk + c * 16);
-        const uint32_t w4[4] = {wv.x >> nib_shift, wv.y >> nib_shift, wv.z >> nib_shift, wv.w >> nib_shift};
-        // scale / offset half2 for the k pairs (2r, 2r+1) [lo] and (2r+8, 2r+9) [hi] of word r
-        uint32_t s_lo[4], s_hi[4], o_lo[4], o_hi[4];
-        if (COLWISE) {
-          // scale tile: meta_rows x 128 fp16; the 16 k of a chunk share one block
-          const int mr = (p.block >= BLOCK_K) ? 0 : ((c * 16) >> p.block_shift);
-          const uint32_t sc = reinterpret_cast<const unsigned short*>(sc_tile)[mr * TILE_N + n_l];
-          const uint32_t z = p.has_zp ? (uint32_t)zp_tile[mr * TILE_N + n_l] : 8u;
-          const uint32_t sc2 = sc | (sc << 16);
-          // fp16(-16 - z) by bit placement (0xcc00 is -16.0, mantissa step 1/64), times the scale
-          const uint32_t nz = 0xcc00u | (z << 6);
-          const uint32_t of2 = hmul2_u32(sc2, nz | (nz << 16));
-#pragma unroll
-          for (int r = 0; r < 4; ++r) {
-            s_lo[r] = s_hi[r] = sc2;
-            o_lo[r] = o_hi[r] = of2;
-          }
-        } else {
-          // scale tile: (128 / block) rows x 64 k fp16, k permuted per 16 as
-          // 0 1 8 9 2 3 10 11 ...; zero points 0 8 1 9 2 10 3 11 ...
-          const int mr = n_l / p.block;
-          const uint4* sp = reinterpret_cast<const uint4*>(sc_tile + mr * 128 + c * 32);
-          const uint4 s0 = sp[0], s1 = sp[1];
-          const uint32_t sw[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-          uint4 zv = make_uint4(0x08080808u, 0x08080808u, 0x08080808u, 0x08080808u);
-          if (p.has_zp) zv = *reinterpret_cast<const uint4*>(zp_tile + mr * 64 + c * 16);
-          const uint32_t zw[4] = {zv.x, zv.y, zv.z, zv.w};
-#pragma unroll
-          for (int r = 0; r < 4; ++r) {
-            s_lo[r] = sw[2 * r];
-            s_hi[r] = sw[2 * r + 1];
-            const uint32_t nz_lo = ((zw[r] << 6) & 0x03c003c0u) | 0xcc00cc00u;  // fp16(-16 - z)
-            const uint32_t nz_hi = ((zw[r] >> 2) & 0x03c003c0u) | 0xcc00cc00u;
-            o_lo[r] = hmul2_u32(sw[2 * r], nz_lo);
-            o_hi[r] = hmul2_u32(sw[2 * r + 1], nz_hi);
-          }
-        }
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-          // after the shift this thread's nibbles sit where column n0's do: bits 0-3 / 16-19 hold
-          // k = 2r, 2r+1 and bits 4-7 / 20-23 hold k = 2r+8, 2r+9; fp16(16 + q) by bit placement
-          const uint32_t h_lo = ((w4[r] << 6) & 0x03c003c0u) | 0x4c004c00u;
-          const uint32_t h_hi = ((w4[r] << 2) & 0x03c003c0u) | 0x4c004c00u;
-          const uint32_t d_lo = hfma2_u32(s_lo[r], h_lo, o_lo[r]);
-          const uint32_t d_hi = hfma2_u32(s_hi[r], h_hi, o_hi[r]);
-          // chunk c, word r: k = 16 c + 2 r (+1) -> column 8 c + r; k + 8 -> column 8 c + 4 + r
-          out[8 * c + r] = d_lo;
-          out[8 * c + 4 + r] = d_hi;
-        }
-      }
+      dequant_step<COLWISE>(pk, sc_tile, zp_tile, n_l, nib_shift, p.block, p.block_shift, p.has_zp, out);
       tmem_st_32x32b_x32(tmem_row + (uint32_t)(d * kDeqCols), out);
       tmem_st_wait();
       tc_fence_before();
@@ -686,6 +542,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
                  : "memory");
   }
 }
+
+#include "blkq4_gemm_tc_pair.cuh"
 
 // ---- host side ---------------------------------------------------------------------------
 
@@ -773,9 +631,13 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
     while (p.tmem_cols < need) p.tmem_cols <<= 1;
   }
 
+  // M >= 256: two CTAs per 256 x 256 tile (blkq4_gemm_tc_pair.cuh), each staging half of the activation rows
+  static const bool pair_off = getenv("BLKQ4_TC_NO_PAIR") != nullptr;
+  const bool pair = M >= 256 && !pair_off;
+
   CUtensorMap tm_act, tm_pack, tm_scale, tm_zp;
   bool ok = encode_tensor_map_2d(&tm_act, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a, (uint64_t)K, (uint64_t)M, BLOCK_K,
-                      (uint32_t)p.BM, CU_TENSOR_MAP_SWIZZLE_128B);
+                      pair ? (uint32_t)kPairRows : (uint32_t)p.BM, CU_TENSOR_MAP_SWIZZLE_128B);
   // No swizzle on the packed tile: the dequantizers' 16-byte loads of eight neighbouring packed
   // columns (64 bytes apart) do conflict four ways, but a 64-byte TMA swizzle that removes the
   // conflicts measured 1-2 % SLOWER on the same GPU (c3 59.2 vs 58.2 us): those loads are not on
@@ -802,6 +664,43 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
   if (!ok) return "cuTensorMapEncodeTiled failed";
 
   const int sms = sm_count();
+  if (pair) {
+    p.k_steps = K / BLOCK_K;
+    p.num_items = p.m_tiles * ((p.n_tiles + 1) / 2);
+    auto kern = colwise ? gemm_tc_pair_kernel<true, kPairWeightStages> : gemm_tc_pair_kernel<false, kPairWeightStages>;
+    const SmemPlan plan = make_plan(kPairRows, kPairWeightStages);
+    static std::atomic<int> granted[2][64];
+    cudaError_t e = ensure_dynamic_smem(kern, plan.total, granted[colwise ? 1 : 0]);
+    if (e != cudaSuccess) return std::string(cudaGetErrorString(e));
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = plan.total;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    // pairs that can be resident at once (the cluster size is part of the kernel): one per two SMs at best
+    static std::atomic<int> max_pairs[2][64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    int pairs = (dev >= 0 && dev < 64) ? max_pairs[colwise ? 1 : 0][dev].load(std::memory_order_relaxed) : 0;
+    if (pairs <= 0) {
+      cfg.gridDim = dim3(sms & ~1);
+      cfg.numAttrs = 0;
+      int n = 0;
+      e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+      if (e != cudaSuccess || n <= 0) { cudaGetLastError(); n = sms / 2; }
+      pairs = n < sms / 2 ? n : sms / 2;
+      if (dev >= 0 && dev < 64) max_pairs[colwise ? 1 : 0][dev].store(pairs, std::memory_order_relaxed);
+    }
+    cfg.numAttrs = (flags & BLKQ4_GEMM_EARLY_WEIGHT_FETCH) ? 1 : 0;
+    cfg.gridDim = dim3(2 * (p.num_items < pairs ? p.num_items : pairs));
+    e = cudaLaunchKernelEx(&cfg, kern, tm_act, tm_pack, tm_scale, tm_zp, p);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    if (e != cudaSuccess) return std::string(cudaGetErrorString(e));
+    return std::string();
+  }
   const int num_tiles = p.m_tiles * p.n_tiles;
   const SplitPlan sp = (workspace && reinterpret_cast<uintptr_t>(workspace) % 256 == 0)
                            ? plan_split(M, N, K, workspace_bytes) : SplitPlan{0, 0, 0, 0};
@@ -814,8 +713,8 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
   p.ws_flags = reinterpret_cast<unsigned*>(workspace);
   p.ws_partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + sp.flags_bytes);
   const int grid = p.num_items < sms ? p.num_items : sms;
-  const SmemPlan plan = make_plan(p.BM);
-  auto kern = colwise ? gemm_tc_kernel<true> : gemm_tc_kernel<false>;
+  const SmemPlan plan = make_plan(p.BM, 6);
+  auto kern = colwise ? gemm_tc_kernel<true, 6> : gemm_tc_kernel<false, 6>;
   static std::atomic<int> granted[2][64];
   cudaError_t e = ensure_dynamic_smem(kern, plan.total, granted[colwise ? 1 : 0]);
   if (e != cudaSuccess) return std::string(cudaGetErrorString(e));

@@ -1,0 +1,361 @@
+// CTA-pair variant of the tensor-core W4A16 GEMM (M >= 256).  Included by blkq4_gemm_tc.cu inside its
+// anonymous namespace: it shares that file's Params, ring constants, barrier slots and error word.
+//
+// Why pairs.  With one CTA per tile a 64-k step stages 32 KB of activations (256 rows) in shared
+// memory and the four MMAs read them back: 72 KB of shared-memory traffic per step against the
+// 64 KB the SM can move in the 512 cycles the tensor pipe needs, so the step takes ~650 cycles.
+// Two CTAs of a cluster (`cta_group::2`) compute one 256 (weight columns) x 256 (activation rows)
+// tile together: each dequantizes ITS 128 weight columns into its own tensor memory and stages only
+// ITS 128 activation rows; the pair's MMA (M = 256, N = 256, issued by the even CTA alone) reads
+// every activation row once, from the CTA that holds it, for both halves of the weights.  Per SM and
+// step: 16 KB of activations written, 16 KB read.
+//
+// Protocol (leader = cluster rank 0; every barrier the MMA thread waits on lives in the leader):
+//   ACT_FULL[s]   count 1: the leader's activation producer arrives with expect_tx of BOTH halves;
+//                 both producers issue their TMA load with .cta_group::2, which lets the copy into
+//                 the peer's own shared memory complete its bytes on the leader's barrier.
+//   DEQ_FULL[d]   count 8: four dequantizer warps of each CTA (the peer's arrive remotely).
+//   MMA_DONE[g]   tcgen05.commit with a two-CTA multicast: the copy in each CTA frees that CTA's
+//                 activation stage and dequantized stage.
+//   ACC_FULL      same multicast commit, to both epilogues; ACC_EMPTY count 8, like DEQ_FULL.
+//   FULL / PACK_FREE (weight ring) stay local to each CTA.
+// The loads here carry no cluster multicast: every CTA copies its own rows.  All waits are bounded;
+// the two CTAs meet at a cluster barrier before either frees its tensor memory or exits.
+
+constexpr int kPairRows = 128;  // activation rows staged per CTA = half of the pair's UMMA N
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `local_addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+// Arrival on a barrier of the peer CTA.  What it publishes lives in tensor memory and is ordered by
+// tcgen05.wait::st / tcgen05.fence::before_thread_sync, so the arrive carries no cluster-scope release
+// (measured: with .release.cluster the peer's dequantizer warps took 2.7x as long per step).
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait with cluster-scope acquire (the arrivals may come from the peer CTA).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int who) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      *abort_flag = 1;
+      atomicCAS(&g_gemm_tc_error, 0, who);
+      return false;
+    }
+  }
+}
+// TMA load into THIS CTA's shared memory whose byte count completes on `bar_cluster_addr`, a barrier of
+// either CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                                 uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
+      : "memory");
+}
+// The four pair MMAs of one 64-k step (see umma_f16_ts_x4).
+__device__ __forceinline__ void umma_f16_ts_x4_pair(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                                    uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 b0, b1, b2, b3;\n\t.reg .b32 l1, l2, l3, a1, a2, a3;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "setp.eq.b32 q, 0, 0;\n\t"
+      "add.u32 l1, %2, 2;\n\tadd.u32 l2, %2, 4;\n\tadd.u32 l3, %2, 6;\n\t"
+      "add.u32 a1, %1, 8;\n\tadd.u32 a2, %1, 16;\n\tadd.u32 a3, %1, 24;\n\t"
+      "mov.b64 b0, {%2, %3};\n\tmov.b64 b1, {l1, %3};\n\tmov.b64 b2, {l2, %3};\n\tmov.b64 b3, {l3, %3};\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], b0, %4, p;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [a1], b1, %4, q;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [a2], b2, %4, q;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [a3], b3, %4, q;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives (once every earlier MMA of the pair has retired) on the barrier at this offset in both CTAs.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  const uint16_t both = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"(both)
+      : "memory");
+}
+
+template <bool COLWISE, int WS>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_pack,
+                    const __grid_constant__ CUtensorMap tm_scale, const __grid_constant__ CUtensorMap tm_zp,
+                    const Params p) {
+  BLKQ4_TC_BARRIER_SLOTS(WS)
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const SmemPlan plan = make_plan(kPairRows, kStages);
+  const uint32_t act_stride = (plan.act_bytes + 1023u) & ~1023u;
+  const uint32_t bars = base + plan.bars;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + plan.bars + BAR_COUNT * 8);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + plan.bars + BAR_COUNT * 8 + 8);
+  auto bar = [&](int id) { return bars + 8u * (uint32_t)id; };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = (int)(blockIdx.x >> 1), num_pairs = (int)(gridDim.x >> 1);
+  constexpr uint32_t kTmemCols = 512;  // 256 accumulator columns + eight dequantized stages of 32
+  constexpr uint32_t kAcol0 = 256;
+  asm volatile("griddepcontrol.launch_dependents;");
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kActStages; ++i) mbar_init(bar(BAR_ACT_FULL + i), 1);
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(bar(BAR_FULL + i), 1);
+      mbar_init(bar(BAR_PACK_FREE + i), kWarpsPerDeqGroup);
+    }
+    for (int i = 0; i < kDeqStages; ++i) mbar_init(bar(BAR_DEQ_FULL + i), 2 * kWarpsPerDeqGroup);
+    for (int i = 0; i < kDoneBars; ++i) mbar_init(bar(BAR_MMA_DONE + i), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(BAR_ACC_FULL + i), 1);
+      mbar_init(bar(BAR_ACC_EMPTY + i), 2 * kNumEpiWarps);
+    }
+    *abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == 1) {
+    // one warp of EACH CTA of the pair, same warp index, same destination offset
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything of this CTA signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int k_steps = p.k_steps;
+
+  if (warp == 0) {
+    // ========================= TMA producer: this CTA's 128 activation rows ========================
+    if (lane == 0) {
+      asm volatile("griddepcontrol.wait;" ::: "memory");  // activations belong to stream order
+      uint32_t it = 0;
+      for (int item = pair; item < p.num_items; item += num_pairs) {
+        const int m_tile = item % p.m_tiles;
+        for (int ks = 0; ks < k_steps; ++ks, ++it) {
+          const int sa = it % kActStages;
+          if (it >= (uint32_t)kActStages) {
+            const uint32_t g = (it - kActStages) / kCommitSteps;
+            if (!mbar_wait(bar(BAR_MMA_DONE + g % kDoneBars), (g / kDoneBars) & 1, abort_flag, 0x100 | sa))
+              goto act_producer_done;
+          }
+          const uint32_t fb = bar(BAR_ACT_FULL + sa);
+          if (rank == 0) mbar_arrive_expect_tx(fb, 2u * plan.act_bytes);
+          tma_load_2d_pair(base + plan.act + sa * act_stride, &tm_act, ks * BLOCK_K,
+                           m_tile * 2 * kPairRows + (int)rank * kPairRows, map_to_cta(fb, 0));
+        }
+      }
+    act_producer_done:;
+    }
+  } else if (warp == kWeightProducerWarp) {
+    // ==================== TMA producer: this CTA's packed weights and meta =================
+    if (lane == 0) {
+      const uint32_t tx = kPackTileBytes + (uint32_t)p.meta_rows * p.meta_row_bytes_s +
+                          (p.has_zp ? (uint32_t)p.meta_rows * p.meta_row_bytes_z : 0u);
+      uint32_t it = 0;
+      for (int item = pair; item < p.num_items; item += num_pairs) {
+        const int n_tile = 2 * (item / p.m_tiles) + (int)rank;
+        for (int ks = 0; ks < k_steps; ++ks, ++it) {
+          const int s = it % kStages;
+          if (it >= (uint32_t)kStages &&
+              !mbar_wait(bar(BAR_PACK_FREE + s), ((it / kStages) - 1) & 1, abort_flag, 0x110 | s))
+            goto w_producer_done;
+          const uint32_t fb = bar(BAR_FULL + s);
+          mbar_arrive_expect_tx(fb, tx);
+          const int k0 = ks * BLOCK_K;
+          tma_load_2d(base + plan.pack + s * kPackTileBytes, &tm_pack, k0, n_tile * (TILE_N / 2), fb);
+          if (COLWISE) {
+            const int mrow = k0 >> p.block_shift;
+            tma_load_2d(base + plan.scale + s * kScaleTileBytes, &tm_scale, n_tile * TILE_N, mrow, fb);
+            if (p.has_zp) tma_load_2d(base + plan.zp + s * kZpTileBytes, &tm_zp, n_tile * TILE_N, mrow, fb);
+          } else {
+            const int mrow = (n_tile * TILE_N) >> p.block_shift;
+            tma_load_2d(base + plan.scale + s * kScaleTileBytes, &tm_scale, k0, mrow, fb);
+            if (p.has_zp) tma_load_2d(base + plan.zp + s * kZpTileBytes, &tm_zp, k0, mrow, fb);
+          }
+        }
+      }
+    w_producer_done:;
+    }
+  } else if (warp == 1) {
+    // =============================== MMA issuer: the leader's lane 0 =================================
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = make_idesc_f16(2 * TILE_N, 2 * kPairRows);
+      const uint32_t desc_hi = (uint32_t)(make_sw128_kmajor_desc(0) >> 32);
+      const uint32_t desc_lo_flags = (uint32_t)(make_sw128_kmajor_desc(0) & 0xFFFFFFFFu);
+      const uint32_t act_lo0 = desc_lo_flags | (((base + plan.act) >> 4) & 0x3FFFu);
+      const uint32_t act_lo_step = act_stride >> 4;
+      const uint32_t a_tmem0 = tmem_base + kAcol0;
+      uint32_t s = 0, sa = 0, par_s = 0, par_sa = 0, gdone = 0, it = 0, tcount = 0;
+#ifdef BLKQ4_TC_PAIR_DEBUG
+      long long dbg_a = 0, dbg_d = 0, dbg_e = 0, dbg_t0 = clock64(), dbg_x;
+#define DBG_T(acc, stmt) dbg_x = clock64(); stmt; acc += clock64() - dbg_x;
+#else
+#define DBG_T(acc, stmt) stmt;
+#endif
+      for (int item = pair; item < p.num_items; item += num_pairs, ++tcount) {
+        DBG_T(dbg_e, if (tcount >= 1u && !mbar_wait_cluster(bar(BAR_ACC_EMPTY), (tcount - 1u) & 1u, abort_flag, 0x200)) goto mma_done)
+        tc_fence_after();
+        for (int ks = 0; ks < k_steps; ++ks, ++it) {
+          const uint32_t bar_a = bar(BAR_ACT_FULL) + 8u * sa, bar_d = bar(BAR_DEQ_FULL) + 8u * s;
+          DBG_T(dbg_a, if (!mbar_try_wait(bar_a, par_sa) && !mbar_wait(bar_a, par_sa, abort_flag, 0x210 | sa)) goto mma_done)
+          DBG_T(dbg_d, if (!mbar_try_wait(bar_d, par_s) && !mbar_wait(bar_d, par_s, abort_flag, 0x220 | s)) goto mma_done)
+          tc_fence_after();
+          umma_f16_ts_x4_pair(tmem_base, a_tmem0 + s * kDeqCols, act_lo0 + sa * act_lo_step, desc_hi, idesc,
+                              ks > 0 ? 1u : 0u);
+          if (it % kCommitSteps == kCommitSteps - 1) {
+            umma_commit_pair(bar(BAR_MMA_DONE) + 8u * gdone);
+            if (++gdone == kDoneBars) gdone = 0;
+          }
+          if (++s == kDeqStages) { s = 0; par_s ^= 1u; }
+          if (++sa == kActStages) { sa = 0; par_sa ^= 1u; }
+        }
+        umma_commit_pair(bar(BAR_ACC_FULL));
+      }
+#ifdef BLKQ4_TC_PAIR_DEBUG
+      if (pair == 0 || pair == 40)
+        printf("pair %d: steps %u total %lld wait_act %lld wait_deq %lld wait_acc_empty %lld\n", pair, it,
+               clock64() - dbg_t0, dbg_a, dbg_d, dbg_e);
+#endif
+#undef DBG_T
+    mma_done:;
+    }
+  } else if (warp < 2 + kNumEpiWarps) {
+    // =============================== epilogue: this CTA's 128 weight columns ===================================
+    const int quarter = warp & 3;
+    uint32_t tcount = 0;
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // the output belongs to stream order
+    const uint32_t acc_empty_leader = map_to_cta(bar(BAR_ACC_EMPTY), 0);
+    for (int item = pair; item < p.num_items; item += num_pairs, ++tcount) {
+      const int n_tile = 2 * (item / p.m_tiles) + (int)rank, m_tile = item % p.m_tiles;
+      if (!mbar_wait_cluster(bar(BAR_ACC_FULL), tcount & 1u, abort_flag, 0x300)) break;
+      tc_fence_after();
+      const int n = n_tile * TILE_N + quarter * 32 + lane;
+      const int m0 = m_tile * 2 * kPairRows;
+      const int odd = lane & 1;
+      const bool n_ok = (n | 1) < p.N;
+      for (int c0 = 0; c0 < 2 * kPairRows; c0 += 32) {
+        if (m0 + c0 >= p.M) break;  // warp-uniform
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
+        tmem_ld_wait();
+        int m = m0 + c0 + odd;
+        __half* dst = p.out + (size_t)m * p.N + (n & ~1);
+        const bool add_bias = p.bias != nullptr && n_ok;
+        const __half2 bias2 = add_bias ? *reinterpret_cast<const __half2*>(p.bias + (n & ~1)) : __half2();
+        const size_t row_step = 2 * (size_t)p.N;
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          const float mine = __uint_as_float(odd ? r[j + 1] : r[j]);
+          const float give = __uint_as_float(odd ? r[j] : r[j + 1]);
+          const float got = __shfl_xor_sync(0xffffffffu, give, 1);
+          __half2 v = odd ? __floats2half2_rn(got, mine) : __floats2half2_rn(mine, got);
+          if (add_bias) v = __hadd2(v, bias2);
+          if (n_ok && m < p.M) *reinterpret_cast<__half2*>(dst) = v;
+          dst += row_step;
+          m += 2;
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (rank == 0) mbar_arrive(bar(BAR_ACC_EMPTY));
+        else mbar_arrive_remote(acc_empty_leader);
+      }
+    }
+  } else if (warp < kWeightProducerWarp) {
+    // =============================== dequantizers: this CTA's 128 weight columns ===============================
+    const int dw = warp - (2 + kNumEpiWarps);
+    const int group = dw / kWarpsPerDeqGroup;
+    const int n_l = 32 * (warp & 3) + lane;
+    const int np_l = 8 * (n_l >> 4) + (n_l & 7);
+    const uint32_t nib_shift = (n_l & 8) ? 8u : 0u;
+    const uint32_t tmem_row = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + kAcol0;
+    const uint32_t deq_full_leader = map_to_cta(bar(BAR_DEQ_FULL), 0);
+    int my_items = 0;
+    for (int item = pair; item < p.num_items; item += num_pairs) ++my_items;
+    const uint32_t total_its = (uint32_t)my_items * (uint32_t)k_steps;
+#ifdef BLKQ4_TC_PAIR_DEBUG
+    long long dq_m = 0, dq_f = 0, dq_t0 = clock64(), dq_x;
+#endif
+    for (uint32_t it = group; it < total_its; it += kDeqGroups) {
+      const int s = it % kStages, d = it % kDeqStages;
+#ifdef BLKQ4_TC_PAIR_DEBUG
+      dq_x = clock64();
+#endif
+      if (it >= (uint32_t)kDeqStages) {
+        const uint32_t g = (it - kDeqStages) / kCommitSteps;
+        if (!mbar_wait(bar(BAR_MMA_DONE + g % kDoneBars), (g / kDoneBars) & 1, abort_flag, 0x410 | d)) break;
+      }
+#ifdef BLKQ4_TC_PAIR_DEBUG
+      dq_m += clock64() - dq_x; dq_x = clock64();
+#endif
+      if (!mbar_wait(bar(BAR_FULL + s), (it / kStages) & 1, abort_flag, 0x400 | s)) break;
+#ifdef BLKQ4_TC_PAIR_DEBUG
+      dq_f += clock64() - dq_x;
+#endif
+      tc_fence_after();
+      const uint8_t* pk = base_ptr + plan.pack + s * kPackTileBytes + np_l * 64;
+      const uint8_t* sc_tile = base_ptr + plan.scale + s * kScaleTileBytes;
+      const uint8_t* zp_tile = base_ptr + plan.zp + s * kZpTileBytes;
+      uint32_t out[32];
+      dequant_step<COLWISE>(pk, sc_tile, zp_tile, n_l, nib_shift, p.block, p.block_shift, p.has_zp, out);
+      tmem_st_32x32b_x32(tmem_row + (uint32_t)(d * kDeqCols), out);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (rank == 0) mbar_arrive(bar(BAR_DEQ_FULL + d));
+        else mbar_arrive_remote(deq_full_leader + 8u * (uint32_t)d);
+        mbar_arrive(bar(BAR_PACK_FREE + s));
+      }
+    }
+#ifdef BLKQ4_TC_PAIR_DEBUG
+    if (pair == 0 && (warp & 3) == 0 && lane == 0)
+      printf("deq rank %u group %d: total %lld wait_mma_done %lld wait_weights %lld\n", rank, group, clock64() - dq_t0, dq_m, dq_f);
+#endif
+  }
+
+  // ---- teardown: neither CTA frees tensor memory or leaves while the other may still signal it ----
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) __nanosleep(50000);  // let copies in flight land
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
