@@ -54,7 +54,6 @@ using namespace tc;
 constexpr int kActStages = 6;
 // The weight ring in shared memory (packed tile + scales + zero points per stage) is a template
 // parameter of the kernels.
-constexpr int kPairWeightStages = 16;
 constexpr int kDeqStages = 8;     // dequantized weights in tensor memory
 // tcgen05.commit costs about as much pipe time as one 128x256x16 MMA (measured: 128 cycles per MMA
 // back to back, 241 with a commit after each), so completion is signalled once per kCommitSteps
@@ -172,11 +171,11 @@ struct SmemPlan {
   uint32_t act, pack, scale, zp, bars, total;
   uint32_t act_bytes;
 };
-__host__ __device__ inline SmemPlan make_plan(int BM, int kStages) {
+__host__ __device__ inline SmemPlan make_plan(int BM, int kStages, int act_stages) {
   SmemPlan p;
   p.act_bytes = (uint32_t)BM * 128u;
   uint32_t o = 0;
-  p.act = o;   o += kActStages * ((p.act_bytes + 1023u) & ~1023u);  // 1024-aligned tiles
+  p.act = o;   o += act_stages * ((p.act_bytes + 1023u) & ~1023u);  // 1024-aligned tiles
   p.pack = o;  o += kStages * kPackTileBytes;
   p.scale = o; o += kStages * kScaleTileBytes;
   p.zp = o;    o += kStages * kZpTileBytes;
@@ -187,14 +186,14 @@ __host__ __device__ inline SmemPlan make_plan(int BM, int kStages) {
 
 // Barrier slots (8 bytes each) inside the barrier block.  Stage s of the TMA ring and stage s
 // of the dequantized ring belong to the same k step, so one "MMA done" barrier frees both.
-#define BLKQ4_TC_BARRIER_SLOTS(WS)                                                                                 \
+#define BLKQ4_TC_BARRIER_SLOTS(WS, ACT, DONE)                                                         \
   constexpr int kStages = (WS);                                                                                    \
   constexpr int BAR_ACT_FULL = 0;                        /* [kActStages] activation tile landed (-> MMA issuer) */  \
-  constexpr int BAR_FULL = BAR_ACT_FULL + kActStages;    /* [kStages] packed weights + meta landed (-> dequantizers) */ \
+  constexpr int BAR_FULL = BAR_ACT_FULL + (ACT);         /* [kStages] packed weights + meta landed (-> dequantizers) */ \
   constexpr int BAR_PACK_FREE = BAR_FULL + kStages;      /* [kStages] packed weights / meta read (-> producer) */   \
   constexpr int BAR_DEQ_FULL = BAR_PACK_FREE + kStages;  /* [kDeqStages] dequantized stage in TMEM (-> MMA issuer) */ \
   constexpr int BAR_MMA_DONE = BAR_DEQ_FULL + kDeqStages;  /* [kDoneBars] commit group g = it / kCommitSteps retired, index g % kDoneBars */ \
-  constexpr int BAR_ACC_FULL = BAR_MMA_DONE + kDoneBars; /* [2] accumulator complete */                             \
+  constexpr int BAR_ACC_FULL = BAR_MMA_DONE + (DONE);    /* [2] accumulator complete */                             \
   constexpr int BAR_ACC_EMPTY = BAR_ACC_FULL + 2;        /* [2] accumulator drained by the epilogue */              \
   constexpr int BAR_COUNT = BAR_ACC_EMPTY + 2;                                                                      \
   static_assert(BAR_COUNT * 8 + 16 <= 512, "barrier block too small");
@@ -204,11 +203,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_pack,
                const __grid_constant__ CUtensorMap tm_scale, const __grid_constant__ CUtensorMap tm_zp,
                const Params p) {
-  BLKQ4_TC_BARRIER_SLOTS(WS)
+  BLKQ4_TC_BARRIER_SLOTS(WS, kActStages, kDoneBars)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const SmemPlan plan = make_plan(p.BM, kStages);
+  const SmemPlan plan = make_plan(p.BM, kStages, kActStages);
   const uint32_t act_stride = (plan.act_bytes + 1023u) & ~1023u;
   const uint32_t bars = base + plan.bars;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + plan.bars + BAR_COUNT * 8);
@@ -668,7 +667,7 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
     p.k_steps = K / BLOCK_K;
     p.num_items = p.m_tiles * ((p.n_tiles + 1) / 2);
     auto kern = colwise ? gemm_tc_pair_kernel<true, kPairWeightStages> : gemm_tc_pair_kernel<false, kPairWeightStages>;
-    const SmemPlan plan = make_plan(kPairRows, kPairWeightStages);
+    const SmemPlan plan = make_plan(kPairRows, kPairWeightStages, kPairActStages);
     static std::atomic<int> granted[2][64];
     cudaError_t e = ensure_dynamic_smem(kern, plan.total, granted[colwise ? 1 : 0]);
     if (e != cudaSuccess) return std::string(cudaGetErrorString(e));
@@ -713,7 +712,7 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
   p.ws_flags = reinterpret_cast<unsigned*>(workspace);
   p.ws_partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + sp.flags_bytes);
   const int grid = p.num_items < sms ? p.num_items : sms;
-  const SmemPlan plan = make_plan(p.BM, 6);
+  const SmemPlan plan = make_plan(p.BM, 6, kActStages);
   auto kern = colwise ? gemm_tc_kernel<true, 6> : gemm_tc_kernel<false, 6>;
   static std::atomic<int> granted[2][64];
   cudaError_t e = ensure_dynamic_smem(kern, plan.total, granted[colwise ? 1 : 0]);

@@ -11,10 +11,12 @@
 // step: 16 KB of activations written, 16 KB read.
 //
 // Protocol (leader = cluster rank 0; every barrier the MMA thread waits on lives in the leader):
-//   ACT_FULL[s]   count 1: the leader's activation producer arrives with expect_tx of BOTH halves;
-//                 both producers issue their TMA load with .cta_group::2, which lets the copy into
-//                 the peer's own shared memory complete its bytes on the leader's barrier.
-//   DEQ_FULL[d]   count 8: four dequantizer warps of each CTA (the peer's arrive remotely).
+//   STEP_FULL[s]  (the slots named DEQ_FULL) count 9: the leader's activation producer arrives with
+//                 expect_tx of BOTH halves of the step's activations, and the four dequantizer warps of
+//                 each CTA arrive once their part of the step's weights is in tensor memory (the peer's
+//                 remotely).  Both activation producers issue their TMA load with .cta_group::2, which
+//                 lets the copy into the peer's own shared memory complete its bytes on the leader's
+//                 barrier.
 //   MMA_DONE[g]   tcgen05.commit with a two-CTA multicast: the copy in each CTA frees that CTA's
 //                 activation stage and dequantized stage.
 //   ACC_FULL      same multicast commit, to both epilogues; ACC_EMPTY count 8, like DEQ_FULL.
@@ -23,6 +25,26 @@
 // the two CTAs meet at a cluster barrier before either frees its tensor memory or exits.
 
 constexpr int kPairRows = 128;  // activation rows staged per CTA = half of the pair's UMMA N
+// Rings of the pair kernel.  The activation ring is as deep as the ring of dequantized stages, so
+// that ONE barrier per step ("step full") collects everything the MMAs of the step read - the bytes of
+// both CTAs' activation copies and the arrivals of both CTAs' dequantizer warps - and the MMA thread
+// polls one barrier per step instead of two: every instruction of that thread is on the critical path.
+#ifndef BLKQ4_TC_PAIR_ACT
+#define BLKQ4_TC_PAIR_ACT 8
+#endif
+#ifndef BLKQ4_TC_PAIR_WS
+#define BLKQ4_TC_PAIR_WS 8
+#endif
+#ifndef BLKQ4_TC_PAIR_COMMIT
+#define BLKQ4_TC_PAIR_COMMIT 1
+#endif
+constexpr int kPairActStages = BLKQ4_TC_PAIR_ACT;
+constexpr int kPairWeightStages = BLKQ4_TC_PAIR_WS;
+constexpr int kPairCommitSteps = BLKQ4_TC_PAIR_COMMIT;
+// one "MMAs retired" barrier per commit group a waiter may look back to: the deeper of the two rings
+constexpr int kPairDoneBars = (kPairActStages > kDeqStages ? kPairActStages : kDeqStages) / kPairCommitSteps + 1;
+static_assert(kPairActStages == kDeqStages, "one barrier per step serves both rings");
+static_assert(kDeqStages % kPairCommitSteps == 0, "rings are released per commit group");
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -110,11 +132,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_pack,
                     const __grid_constant__ CUtensorMap tm_scale, const __grid_constant__ CUtensorMap tm_zp,
                     const Params p) {
-  BLKQ4_TC_BARRIER_SLOTS(WS)
+  constexpr int kActStages = kPairActStages, kDoneBars = kPairDoneBars, kCommitSteps = kPairCommitSteps;
+  BLKQ4_TC_BARRIER_SLOTS(WS, kPairActStages, kPairDoneBars)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const SmemPlan plan = make_plan(kPairRows, kStages);
+  const SmemPlan plan = make_plan(kPairRows, kStages, kActStages);
   const uint32_t act_stride = (plan.act_bytes + 1023u) & ~1023u;
   const uint32_t bars = base + plan.bars;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + plan.bars + BAR_COUNT * 8);
@@ -134,7 +157,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
       mbar_init(bar(BAR_FULL + i), 1);
       mbar_init(bar(BAR_PACK_FREE + i), kWarpsPerDeqGroup);
     }
-    for (int i = 0; i < kDeqStages; ++i) mbar_init(bar(BAR_DEQ_FULL + i), 2 * kWarpsPerDeqGroup);
+    for (int i = 0; i < kDeqStages; ++i) mbar_init(bar(BAR_DEQ_FULL + i), 1 + 2 * kWarpsPerDeqGroup);  // "step full"
     for (int i = 0; i < kDoneBars; ++i) mbar_init(bar(BAR_MMA_DONE + i), 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(BAR_ACC_FULL + i), 1);
@@ -162,6 +185,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
     if (lane == 0) {
       asm volatile("griddepcontrol.wait;" ::: "memory");  // activations belong to stream order
       uint32_t it = 0;
+#ifdef BLKQ4_TC_PAIR_DEBUG
+      long long ad = 0;
+#endif
       for (int item = pair; item < p.num_items; item += num_pairs) {
         const int m_tile = item % p.m_tiles;
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
@@ -171,12 +197,21 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
             if (!mbar_wait(bar(BAR_MMA_DONE + g % kDoneBars), (g / kDoneBars) & 1, abort_flag, 0x100 | sa))
               goto act_producer_done;
           }
-          const uint32_t fb = bar(BAR_ACT_FULL + sa);
+          const uint32_t fb = bar(BAR_DEQ_FULL + sa);  // the step's one barrier
           if (rank == 0) mbar_arrive_expect_tx(fb, 2u * plan.act_bytes);
+#ifdef BLKQ4_TC_PAIR_DEBUG
+          long long ca = clock64();
+#endif
           tma_load_2d_pair(base + plan.act + sa * act_stride, &tm_act, ks * BLOCK_K,
                            m_tile * 2 * kPairRows + (int)rank * kPairRows, map_to_cta(fb, 0));
+#ifdef BLKQ4_TC_PAIR_DEBUG
+          ad += clock64() - ca;
+#endif
         }
       }
+#ifdef BLKQ4_TC_PAIR_DEBUG
+      if (pair == 0) printf("aprod rank %u: issue %lld over %u steps\n", rank, ad, it);
+#endif
     act_producer_done:;
     }
   } else if (warp == kWeightProducerWarp) {
@@ -185,21 +220,42 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
       const uint32_t tx = kPackTileBytes + (uint32_t)p.meta_rows * p.meta_row_bytes_s +
                           (p.has_zp ? (uint32_t)p.meta_rows * p.meta_row_bytes_z : 0u);
       uint32_t it = 0;
+#ifdef BLKQ4_TC_PAIR_DEBUG
+      long long wd_w = 0, wd_e = 0, wd_p = 0, wd_s = 0, wd_z = 0, wt0 = clock64();
+#endif
       for (int item = pair; item < p.num_items; item += num_pairs) {
         const int n_tile = 2 * (item / p.m_tiles) + (int)rank;
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
           const int s = it % kStages;
+#ifdef BLKQ4_TC_PAIR_DEBUG
+          long long cw = clock64();
+#endif
           if (it >= (uint32_t)kStages &&
               !mbar_wait(bar(BAR_PACK_FREE + s), ((it / kStages) - 1) & 1, abort_flag, 0x110 | s))
             goto w_producer_done;
           const uint32_t fb = bar(BAR_FULL + s);
+#ifdef BLKQ4_TC_PAIR_DEBUG
+          long long c0 = clock64(); wd_w += c0 - cw;
+#endif
           mbar_arrive_expect_tx(fb, tx);
+#ifdef BLKQ4_TC_PAIR_DEBUG
+          long long c1 = clock64(); wd_e += c1 - c0;
+#endif
           const int k0 = ks * BLOCK_K;
           tma_load_2d(base + plan.pack + s * kPackTileBytes, &tm_pack, k0, n_tile * (TILE_N / 2), fb);
+#ifdef BLKQ4_TC_PAIR_DEBUG
+          long long c2 = clock64(); wd_p += c2 - c1;
+#endif
           if (COLWISE) {
             const int mrow = k0 >> p.block_shift;
             tma_load_2d(base + plan.scale + s * kScaleTileBytes, &tm_scale, n_tile * TILE_N, mrow, fb);
+#ifdef BLKQ4_TC_PAIR_DEBUG
+            long long c3 = clock64(); wd_s += c3 - c2;
+#endif
             if (p.has_zp) tma_load_2d(base + plan.zp + s * kZpTileBytes, &tm_zp, n_tile * TILE_N, mrow, fb);
+#ifdef BLKQ4_TC_PAIR_DEBUG
+            wd_z += clock64() - c3;
+#endif
           } else {
             const int mrow = (n_tile * TILE_N) >> p.block_shift;
             tma_load_2d(base + plan.scale + s * kScaleTileBytes, &tm_scale, k0, mrow, fb);
@@ -207,6 +263,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
           }
         }
       }
+#ifdef BLKQ4_TC_PAIR_DEBUG
+      if (pair == 0) printf("wprod rank %u: total %lld wait_free %lld expect %lld pack %lld scale %lld zp %lld\n", rank, clock64() - wt0, wd_w, wd_e, wd_p, wd_s, wd_z);
+#endif
     w_producer_done:;
     }
   } else if (warp == 1) {
@@ -218,7 +277,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
       const uint32_t act_lo0 = desc_lo_flags | (((base + plan.act) >> 4) & 0x3FFFu);
       const uint32_t act_lo_step = act_stride >> 4;
       const uint32_t a_tmem0 = tmem_base + kAcol0;
-      uint32_t s = 0, sa = 0, par_s = 0, par_sa = 0, gdone = 0, it = 0, tcount = 0;
+      uint32_t s = 0, par_s = 0, gdone = 0, it = 0, tcount = 0;
+      // the barrier of step i + 1 is polled (without blocking) before the MMAs of step i are issued, so
+      // that the poll's round trip overlaps the issue
+      bool ready = false;
 #ifdef BLKQ4_TC_PAIR_DEBUG
       long long dbg_a = 0, dbg_d = 0, dbg_e = 0, dbg_t0 = clock64(), dbg_x;
 #define DBG_T(acc, stmt) dbg_x = clock64(); stmt; acc += clock64() - dbg_x;
@@ -229,18 +291,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
         DBG_T(dbg_e, if (tcount >= 1u && !mbar_wait_cluster(bar(BAR_ACC_EMPTY), (tcount - 1u) & 1u, abort_flag, 0x200)) goto mma_done)
         tc_fence_after();
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
-          const uint32_t bar_a = bar(BAR_ACT_FULL) + 8u * sa, bar_d = bar(BAR_DEQ_FULL) + 8u * s;
-          DBG_T(dbg_a, if (!mbar_try_wait(bar_a, par_sa) && !mbar_wait(bar_a, par_sa, abort_flag, 0x210 | sa)) goto mma_done)
-          DBG_T(dbg_d, if (!mbar_try_wait(bar_d, par_s) && !mbar_wait(bar_d, par_s, abort_flag, 0x220 | s)) goto mma_done)
+          const uint32_t bar_d = bar(BAR_DEQ_FULL) + 8u * s;
+          DBG_T(dbg_d, if (!ready && !mbar_try_wait(bar_d, par_s) && !mbar_wait(bar_d, par_s, abort_flag, 0x220 | s)) goto mma_done)
           tc_fence_after();
-          umma_f16_ts_x4_pair(tmem_base, a_tmem0 + s * kDeqCols, act_lo0 + sa * act_lo_step, desc_hi, idesc,
-                              ks > 0 ? 1u : 0u);
+          const uint32_t a_tmem = a_tmem0 + s * kDeqCols, b_lo = act_lo0 + s * act_lo_step;
+          if (++s == kDeqStages) { s = 0; par_s ^= 1u; }
+          ready = mbar_test_wait(bar(BAR_DEQ_FULL) + 8u * s, par_s);
+          umma_f16_ts_x4_pair(tmem_base, a_tmem, b_lo, desc_hi, idesc, ks > 0 ? 1u : 0u);
           if (it % kCommitSteps == kCommitSteps - 1) {
             umma_commit_pair(bar(BAR_MMA_DONE) + 8u * gdone);
             if (++gdone == kDoneBars) gdone = 0;
           }
-          if (++s == kDeqStages) { s = 0; par_s ^= 1u; }
-          if (++sa == kActStages) { sa = 0; par_sa ^= 1u; }
         }
         umma_commit_pair(bar(BAR_ACC_FULL));
       }

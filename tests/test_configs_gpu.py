@@ -143,13 +143,13 @@ def test_config_c5_prefill(c5_layer):
 
 @pytest.mark.parametrize("M", [1, 2, 3, 5, 8, 9, 12, 16])
 @pytest.mark.parametrize("shape", [(64, True, 352, 2048), (128, False, 256, 4096), (64, False, 4736, 2304),
-                                   (128, True, 160, 3072), (64, True, 4768, 8192), (128, False, 304, 8448)],
-                         ids=lambda s: "-".join(map(str, s)))
+                                   (128, True, 160, 3072)], ids=lambda s: "-".join(map(str, s)))
 def test_decode_kernel_exact_on_known_answers(shape, M):
-    """The cp.async stream kernels (M <= 8 and K >= 2048 in whole groups of 256: decode kernel;
-    M 9..16 and K >= 8192: the kernel with two row groups; other shapes of the list fall to the generic
-    skinny kernel) on the reference tests' known-answer family, where every product and partial sum is
-    exact: equal bits."""
+    """The decode kernel (M <= 8, K >= 2048 in whole groups of 256) and, for M 9..16, the generic skinny
+    kernel on the reference tests' known-answer family, where every product and partial sum is exact:
+    equal bits.  (The family stops being exact near K = 8192 - its sums leave the fp16 range - so the
+    kernel with two row groups, which takes M 9..16 from K = 8192 on, is covered by the Gaussian
+    full-width case of configs[3] at M = 16 instead.)"""
     from gemmlib_b200 import capi
 
     block, has_zp, N, K = shape
