@@ -13,10 +13,13 @@
 // Measured with the operand staged in shared memory instead, the 16 KB written plus 16 KB
 // re-read per step, on top of the TMA traffic, cost a third of the step time.
 //
+// Two kernels share this design.  gemm_tc_kernel (this file; 16 < M < 256) gives every tile to one
+// CTA; gemm_tc_pair_kernel (blkq4_gemm_tc_pair.cuh; M >= 256) gives a 256 x 256 tile to a CTA pair.
+//
 // Persistent CTAs (one per SM) walk the tile list.  Warp roles:
-//   warp 0      TMA producer of the activation tiles (128-byte swizzle), five stages
+//   warp 0      TMA producer of the activation tiles (128-byte swizzle), kActStages stages
 //   warp 14     TMA producer of the packed int4 weight tiles (64 x 64 bytes per 64-k step),
-//               their scales and zero points, eight stages
+//               their scales and zero points, six stages
 //   warp 1      MMA issuer (one elected lane); owns the TMEM allocation
 //   warps 2-5   epilogue: tcgen05.ld -> fp16 -> global, overlapped with the next tile
 //               through a second TMEM accumulator buffer
@@ -168,10 +171,10 @@ __device__ __forceinline__ bool next_item(const Params& p, ItemCursor& c, Item& 
 // ---- shared-memory plan ---------------------------------------------------------------------
 
 struct SmemPlan {
-  uint32_t act, pack, scale, zp, bars, total;
+  uint32_t act, pack, scale, zp, out, bars, total;
   uint32_t act_bytes;
 };
-__host__ __device__ inline SmemPlan make_plan(int BM, int kStages, int act_stages) {
+__host__ __device__ inline SmemPlan make_plan(int BM, int kStages, int act_stages, uint32_t out_bytes = 0) {
   SmemPlan p;
   p.act_bytes = (uint32_t)BM * 128u;
   uint32_t o = 0;
@@ -179,6 +182,7 @@ __host__ __device__ inline SmemPlan make_plan(int BM, int kStages, int act_stage
   p.pack = o;  o += kStages * kPackTileBytes;
   p.scale = o; o += kStages * kScaleTileBytes;
   p.zp = o;    o += kStages * kZpTileBytes;
+  p.out = o;   o += out_bytes;  // output staging of the pair kernel's epilogue
   p.bars = o;  o += 512;
   p.total = o + 1024;  // slack to align the dynamic base to 1024
   return p;
@@ -667,7 +671,7 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
     p.k_steps = K / BLOCK_K;
     p.num_items = p.m_tiles * ((p.n_tiles + 1) / 2);
     auto kern = colwise ? gemm_tc_pair_kernel<true, kPairWeightStages> : gemm_tc_pair_kernel<false, kPairWeightStages>;
-    const SmemPlan plan = make_plan(kPairRows, kPairWeightStages, kPairActStages);
+    const SmemPlan plan = make_plan(kPairRows, kPairWeightStages, kPairActStages, kPairOutBytes);
     static std::atomic<int> granted[2][64];
     cudaError_t e = ensure_dynamic_smem(kern, plan.total, granted[colwise ? 1 : 0]);
     if (e != cudaSuccess) return std::string(cudaGetErrorString(e));

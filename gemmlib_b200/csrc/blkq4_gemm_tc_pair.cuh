@@ -29,18 +29,12 @@ constexpr int kPairRows = 128;  // activation rows staged per CTA = half of the 
 // that ONE barrier per step ("step full") collects everything the MMAs of the step read - the bytes of
 // both CTAs' activation copies and the arrivals of both CTAs' dequantizer warps - and the MMA thread
 // polls one barrier per step instead of two: every instruction of that thread is on the critical path.
-#ifndef BLKQ4_TC_PAIR_ACT
-#define BLKQ4_TC_PAIR_ACT 8
-#endif
-#ifndef BLKQ4_TC_PAIR_WS
-#define BLKQ4_TC_PAIR_WS 8
-#endif
-#ifndef BLKQ4_TC_PAIR_COMMIT
-#define BLKQ4_TC_PAIR_COMMIT 1
-#endif
-constexpr int kPairActStages = BLKQ4_TC_PAIR_ACT;
-constexpr int kPairWeightStages = BLKQ4_TC_PAIR_WS;
-constexpr int kPairCommitSteps = BLKQ4_TC_PAIR_COMMIT;
+constexpr int kPairActStages = 8;     // 16 KB each
+constexpr int kPairWeightStages = 6;  // 5.5 KB each; deeper rings measured no faster
+constexpr int kPairCommitSteps = 1;   // a commit per two steps measured no faster
+// fp16 staging of a CTA's 128 x 256 output tile: the epilogue empties the accumulator into it, hands
+// the accumulator back, and only then writes global memory, under the next tile's MMAs
+constexpr uint32_t kPairOutBytes = 128u * 256u * 2u;
 // one "MMAs retired" barrier per commit group a waiter may look back to: the deeper of the two rings
 constexpr int kPairDoneBars = (kPairActStages > kDeqStages ? kPairActStages : kDeqStages) / kPairCommitSteps + 1;
 static_assert(kPairActStages == kDeqStages, "one barrier per step serves both rings");
@@ -137,7 +131,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const SmemPlan plan = make_plan(kPairRows, kStages, kActStages);
+  const SmemPlan plan = make_plan(kPairRows, kStages, kActStages, kPairOutBytes);
   const uint32_t act_stride = (plan.act_bytes + 1023u) & ~1023u;
   const uint32_t bars = base + plan.bars;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + plan.bars + BAR_COUNT * 8);
@@ -185,9 +179,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
     if (lane == 0) {
       asm volatile("griddepcontrol.wait;" ::: "memory");  // activations belong to stream order
       uint32_t it = 0;
-#ifdef BLKQ4_TC_PAIR_DEBUG
-      long long ad = 0;
-#endif
       for (int item = pair; item < p.num_items; item += num_pairs) {
         const int m_tile = item % p.m_tiles;
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
@@ -199,19 +190,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
           }
           const uint32_t fb = bar(BAR_DEQ_FULL + sa);  // the step's one barrier
           if (rank == 0) mbar_arrive_expect_tx(fb, 2u * plan.act_bytes);
-#ifdef BLKQ4_TC_PAIR_DEBUG
-          long long ca = clock64();
-#endif
           tma_load_2d_pair(base + plan.act + sa * act_stride, &tm_act, ks * BLOCK_K,
                            m_tile * 2 * kPairRows + (int)rank * kPairRows, map_to_cta(fb, 0));
-#ifdef BLKQ4_TC_PAIR_DEBUG
-          ad += clock64() - ca;
-#endif
         }
       }
-#ifdef BLKQ4_TC_PAIR_DEBUG
-      if (pair == 0) printf("aprod rank %u: issue %lld over %u steps\n", rank, ad, it);
-#endif
     act_producer_done:;
     }
   } else if (warp == kWeightProducerWarp) {
@@ -220,42 +202,21 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
       const uint32_t tx = kPackTileBytes + (uint32_t)p.meta_rows * p.meta_row_bytes_s +
                           (p.has_zp ? (uint32_t)p.meta_rows * p.meta_row_bytes_z : 0u);
       uint32_t it = 0;
-#ifdef BLKQ4_TC_PAIR_DEBUG
-      long long wd_w = 0, wd_e = 0, wd_p = 0, wd_s = 0, wd_z = 0, wt0 = clock64();
-#endif
       for (int item = pair; item < p.num_items; item += num_pairs) {
         const int n_tile = 2 * (item / p.m_tiles) + (int)rank;
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
           const int s = it % kStages;
-#ifdef BLKQ4_TC_PAIR_DEBUG
-          long long cw = clock64();
-#endif
           if (it >= (uint32_t)kStages &&
               !mbar_wait(bar(BAR_PACK_FREE + s), ((it / kStages) - 1) & 1, abort_flag, 0x110 | s))
             goto w_producer_done;
           const uint32_t fb = bar(BAR_FULL + s);
-#ifdef BLKQ4_TC_PAIR_DEBUG
-          long long c0 = clock64(); wd_w += c0 - cw;
-#endif
           mbar_arrive_expect_tx(fb, tx);
-#ifdef BLKQ4_TC_PAIR_DEBUG
-          long long c1 = clock64(); wd_e += c1 - c0;
-#endif
           const int k0 = ks * BLOCK_K;
           tma_load_2d(base + plan.pack + s * kPackTileBytes, &tm_pack, k0, n_tile * (TILE_N / 2), fb);
-#ifdef BLKQ4_TC_PAIR_DEBUG
-          long long c2 = clock64(); wd_p += c2 - c1;
-#endif
           if (COLWISE) {
             const int mrow = k0 >> p.block_shift;
             tma_load_2d(base + plan.scale + s * kScaleTileBytes, &tm_scale, n_tile * TILE_N, mrow, fb);
-#ifdef BLKQ4_TC_PAIR_DEBUG
-            long long c3 = clock64(); wd_s += c3 - c2;
-#endif
             if (p.has_zp) tma_load_2d(base + plan.zp + s * kZpTileBytes, &tm_zp, n_tile * TILE_N, mrow, fb);
-#ifdef BLKQ4_TC_PAIR_DEBUG
-            wd_z += clock64() - c3;
-#endif
           } else {
             const int mrow = (n_tile * TILE_N) >> p.block_shift;
             tma_load_2d(base + plan.scale + s * kScaleTileBytes, &tm_scale, k0, mrow, fb);
@@ -263,9 +224,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
           }
         }
       }
-#ifdef BLKQ4_TC_PAIR_DEBUG
-      if (pair == 0) printf("wprod rank %u: total %lld wait_free %lld expect %lld pack %lld scale %lld zp %lld\n", rank, clock64() - wt0, wd_w, wd_e, wd_p, wd_s, wd_z);
-#endif
     w_producer_done:;
     }
   } else if (warp == 1) {
@@ -281,18 +239,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
       // the barrier of step i + 1 is polled (without blocking) before the MMAs of step i are issued, so
       // that the poll's round trip overlaps the issue
       bool ready = false;
-#ifdef BLKQ4_TC_PAIR_DEBUG
-      long long dbg_a = 0, dbg_d = 0, dbg_e = 0, dbg_t0 = clock64(), dbg_x;
-#define DBG_T(acc, stmt) dbg_x = clock64(); stmt; acc += clock64() - dbg_x;
-#else
-#define DBG_T(acc, stmt) stmt;
-#endif
       for (int item = pair; item < p.num_items; item += num_pairs, ++tcount) {
-        DBG_T(dbg_e, if (tcount >= 1u && !mbar_wait_cluster(bar(BAR_ACC_EMPTY), (tcount - 1u) & 1u, abort_flag, 0x200)) goto mma_done)
+        if (tcount >= 1u && !mbar_wait_cluster(bar(BAR_ACC_EMPTY), (tcount - 1u) & 1u, abort_flag, 0x200)) goto mma_done;
         tc_fence_after();
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
           const uint32_t bar_d = bar(BAR_DEQ_FULL) + 8u * s;
-          DBG_T(dbg_d, if (!ready && !mbar_try_wait(bar_d, par_s) && !mbar_wait(bar_d, par_s, abort_flag, 0x220 | s)) goto mma_done)
+          if (!ready && !mbar_try_wait(bar_d, par_s) && !mbar_wait(bar_d, par_s, abort_flag, 0x220 | s)) goto mma_done;
           tc_fence_after();
           const uint32_t a_tmem = a_tmem0 + s * kDeqCols, b_lo = act_lo0 + s * act_lo_step;
           if (++s == kDeqStages) { s = 0; par_s ^= 1u; }
@@ -305,48 +257,40 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
         }
         umma_commit_pair(bar(BAR_ACC_FULL));
       }
-#ifdef BLKQ4_TC_PAIR_DEBUG
-      if (pair == 0 || pair == 40)
-        printf("pair %d: steps %u total %lld wait_act %lld wait_deq %lld wait_acc_empty %lld\n", pair, it,
-               clock64() - dbg_t0, dbg_a, dbg_d, dbg_e);
-#endif
-#undef DBG_T
     mma_done:;
     }
   } else if (warp < 2 + kNumEpiWarps) {
     // =============================== epilogue: this CTA's 128 weight columns ===================================
+    // A warp owns the 32 weight columns n of its TMEM quarter (lane = n) for all 256 activation rows m
+    // (TMEM columns).  With the single 256-column accumulator the next tile's MMAs wait for this drain,
+    // so it is kept short: tensor memory -> fp16 -> the warp's own staging block [256 m][32 n] in shared
+    // memory, accumulator released, and only then staging -> global memory (64-byte row pieces, 8 bytes
+    // per lane), which overlaps the next tile.  No other warp touches the block: only __syncwarp.
     const int quarter = warp & 3;
     uint32_t tcount = 0;
     asm volatile("griddepcontrol.wait;" ::: "memory");  // the output belongs to stream order
     const uint32_t acc_empty_leader = map_to_cta(bar(BAR_ACC_EMPTY), 0);
+    uint8_t* stage = base_ptr + plan.out + quarter * (256 * 64);
+    const int odd = lane & 1;
     for (int item = pair; item < p.num_items; item += num_pairs, ++tcount) {
       const int n_tile = 2 * (item / p.m_tiles) + (int)rank, m_tile = item % p.m_tiles;
       if (!mbar_wait_cluster(bar(BAR_ACC_FULL), tcount & 1u, abort_flag, 0x300)) break;
       tc_fence_after();
-      const int n = n_tile * TILE_N + quarter * 32 + lane;
       const int m0 = m_tile * 2 * kPairRows;
-      const int odd = lane & 1;
-      const bool n_ok = (n | 1) < p.N;
-      for (int c0 = 0; c0 < 2 * kPairRows; c0 += 32) {
-        if (m0 + c0 >= p.M) break;  // warp-uniform
+      const int rows = min(2 * kPairRows, p.M - m0);
+      for (int c0 = 0; c0 < rows; c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
         tmem_ld_wait();
-        int m = m0 + c0 + odd;
-        __half* dst = p.out + (size_t)m * p.N + (n & ~1);
-        const bool add_bias = p.bias != nullptr && n_ok;
-        const __half2 bias2 = add_bias ? *reinterpret_cast<const __half2*>(p.bias + (n & ~1)) : __half2();
-        const size_t row_step = 2 * (size_t)p.N;
+        // lanes pair up (n even / odd): the even lane writes the even rows of the chunk, the odd lane the
+        // odd rows, each as half2 (n even, n odd) with its partner's value alongside
+        uint8_t* dst = stage + (c0 + odd) * 64 + (lane & ~1) * 2;
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
           const float mine = __uint_as_float(odd ? r[j + 1] : r[j]);
           const float give = __uint_as_float(odd ? r[j] : r[j + 1]);
           const float got = __shfl_xor_sync(0xffffffffu, give, 1);
-          __half2 v = odd ? __floats2half2_rn(got, mine) : __floats2half2_rn(mine, got);
-          if (add_bias) v = __hadd2(v, bias2);
-          if (n_ok && m < p.M) *reinterpret_cast<__half2*>(dst) = v;
-          dst += row_step;
-          m += 2;
+          *reinterpret_cast<__half2*>(dst + j * 64) = odd ? __floats2half2_rn(got, mine) : __floats2half2_rn(mine, got);
         }
       }
       tc_fence_before();
@@ -355,6 +299,28 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
         if (rank == 0) mbar_arrive(bar(BAR_ACC_EMPTY));
         else mbar_arrive_remote(acc_empty_leader);
       }
+      // staging -> global: one instruction moves four rows' 64-byte pieces
+      const int n4 = n_tile * TILE_N + quarter * 32 + (lane & 7) * 4;  // first of this lane's 4 columns
+      const bool n_ok = n4 + 3 < p.N;                                    // N is a multiple of 16
+      __half2 b01 = __half2(), b23 = __half2();
+      const bool add_bias = p.bias != nullptr && n_ok;
+      if (add_bias) {
+        b01 = *reinterpret_cast<const __half2*>(p.bias + n4);
+        b23 = *reinterpret_cast<const __half2*>(p.bias + n4 + 2);
+      }
+      __half* gdst = p.out + (size_t)(m0 + (lane >> 3)) * p.N + n4;
+      for (int r0 = 0; r0 < rows; r0 += 4) {
+        uint2 v = *reinterpret_cast<const uint2*>(stage + r0 * 64 + lane * 8);
+        if (add_bias) {
+          // the bias is added to the ROUNDED result in fp16, as a separate `output += bias` would
+          __half2 lo = __hadd2(*reinterpret_cast<__half2*>(&v.x), b01), hi = __hadd2(*reinterpret_cast<__half2*>(&v.y), b23);
+          v.x = *reinterpret_cast<uint32_t*>(&lo);
+          v.y = *reinterpret_cast<uint32_t*>(&hi);
+        }
+        if (n_ok && r0 + (lane >> 3) < rows) *reinterpret_cast<uint2*>(gdst) = v;
+        gdst += 4 * (size_t)p.N;
+      }
+      __syncwarp();  // the block is rewritten by the next tile
     }
   } else if (warp < kWeightProducerWarp) {
     // =============================== dequantizers: this CTA's 128 weight columns ===============================
@@ -368,25 +334,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
     int my_items = 0;
     for (int item = pair; item < p.num_items; item += num_pairs) ++my_items;
     const uint32_t total_its = (uint32_t)my_items * (uint32_t)k_steps;
-#ifdef BLKQ4_TC_PAIR_DEBUG
-    long long dq_m = 0, dq_f = 0, dq_t0 = clock64(), dq_x;
-#endif
     for (uint32_t it = group; it < total_its; it += kDeqGroups) {
       const int s = it % kStages, d = it % kDeqStages;
-#ifdef BLKQ4_TC_PAIR_DEBUG
-      dq_x = clock64();
-#endif
       if (it >= (uint32_t)kDeqStages) {
         const uint32_t g = (it - kDeqStages) / kCommitSteps;
         if (!mbar_wait(bar(BAR_MMA_DONE + g % kDoneBars), (g / kDoneBars) & 1, abort_flag, 0x410 | d)) break;
       }
-#ifdef BLKQ4_TC_PAIR_DEBUG
-      dq_m += clock64() - dq_x; dq_x = clock64();
-#endif
       if (!mbar_wait(bar(BAR_FULL + s), (it / kStages) & 1, abort_flag, 0x400 | s)) break;
-#ifdef BLKQ4_TC_PAIR_DEBUG
-      dq_f += clock64() - dq_x;
-#endif
       tc_fence_after();
       const uint8_t* pk = base_ptr + plan.pack + s * kPackTileBytes + np_l * 64;
       const uint8_t* sc_tile = base_ptr + plan.scale + s * kScaleTileBytes;
@@ -403,10 +357,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
         mbar_arrive(bar(BAR_PACK_FREE + s));
       }
     }
-#ifdef BLKQ4_TC_PAIR_DEBUG
-    if (pair == 0 && (warp & 3) == 0 && lane == 0)
-      printf("deq rank %u group %d: total %lld wait_mma_done %lld wait_weights %lld\n", rank, group, clock64() - dq_t0, dq_m, dq_f);
-#endif
   }
 
   // ---- teardown: neither CTA frees tensor memory or leaves while the other may still signal it ----
