@@ -64,12 +64,14 @@ constexpr int kDeqStages = 8;     // dequantized weights in tensor memory
 constexpr int kCommitSteps = 1;
 constexpr int kDoneBars = kDeqStages / kCommitSteps;
 static_assert(kActStages % kCommitSteps == 0 && kDeqStages % kCommitSteps == 0, "rings are released per commit group");
-constexpr int kDeqGroups = 2;     // warp groups taking k steps in turn
+constexpr int kDeqGroups = 2;     // warp groups taking k steps in turn (three or four measured 3 % faster at most)
 constexpr int kNumDeqWarps = 4 * kDeqGroups;
 constexpr int kWarpsPerDeqGroup = kNumDeqWarps / kDeqGroups;
 constexpr int kNumEpiWarps = 4;
 constexpr int kWeightProducerWarp = 2 + kNumEpiWarps + kNumDeqWarps;  // last warp
-constexpr int kThreads = 32 * (3 + kNumEpiWarps + kNumDeqWarps);
+constexpr int kSecondIssuerWarp = kWeightProducerWarp + 1;  // second MMA-issuing thread (DUAL kernels), else idle
+constexpr int kMetaProducerWarp = kWeightProducerWarp + 2;  // TMA producer of the scales and zero points
+constexpr int kThreads = 32 * (5 + kNumEpiWarps + kNumDeqWarps);
 constexpr long long kWaitCycles = 4000000000ll;  // ~2 s: far beyond any legitimate wait
 
 struct Params {
@@ -202,7 +204,12 @@ __host__ __device__ inline SmemPlan make_plan(int BM, int kStages, int act_stage
   constexpr int BAR_COUNT = BAR_ACC_EMPTY + 2;                                                                      \
   static_assert(BAR_COUNT * 8 + 16 <= 512, "barrier block too small");
 
-template <bool COLWISE, int WS>
+// DUAL (BM <= 128): two threads issue the MMAs, the even k steps into one accumulator and the odd
+// ones into a second, and the epilogue adds the two.  A thread gets one tcgen05.mma accepted per
+// ~130 cycles whatever its N (measured: N = 32 .. 256, TMEM or shared-memory first operand), while
+// the tensor pipe needs only N/2 cycles for it - two threads with accumulators of their own reach
+// 65 cycles per MMA at N <= 64 and 71 at N = 128.  The sum order is fixed, so results stay reproducible.
+template <bool COLWISE, int WS, bool DUAL>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_pack,
                const __grid_constant__ CUtensorMap tm_scale, const __grid_constant__ CUtensorMap tm_zp,
@@ -230,13 +237,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
   if (threadIdx.x == 0) {
     for (int i = 0; i < kActStages; ++i) mbar_init(bar(BAR_ACT_FULL + i), 1);
     for (int i = 0; i < kStages; ++i) {
-      mbar_init(bar(BAR_FULL + i), 1);
+      mbar_init(bar(BAR_FULL + i), 2);  // the packed-tile producer and the meta producer, each with its bytes
       mbar_init(bar(BAR_PACK_FREE + i), kWarpsPerDeqGroup);
     }
     for (int i = 0; i < kDeqStages; ++i) mbar_init(bar(BAR_DEQ_FULL + i), kWarpsPerDeqGroup);
     for (int i = 0; i < kDoneBars; ++i) mbar_init(bar(BAR_MMA_DONE + i), 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(bar(BAR_ACC_FULL + i), 1);
+      mbar_init(bar(BAR_ACC_FULL + i), DUAL ? 2 : 1);
       mbar_init(bar(BAR_ACC_EMPTY + i), kNumEpiWarps);
     }
     *abort_flag = 0;
@@ -278,11 +285,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       }
     act_producer_done:;
     }
-  } else if (warp == kWeightProducerWarp) {
-    // ==================== TMA producer: packed weights and meta =================
+  } else if (warp == kWeightProducerWarp || warp == kMetaProducerWarp) {
+    // ============ TMA producers: packed weights (one warp), scales and zero points (another) ============
+    // A thread gets one bulk-tensor copy accepted per ~110 cycles; with the stage wait and the byte-count
+    // post, one thread issuing all three copies of a step is good for a step per ~600 cycles, which is
+    // the whole kernel's pace once two threads issue the MMAs.  Hence two producer threads, each
+    // arriving on the stage's barrier with its own byte count.
     if (lane == 0) {
-      const uint32_t tx = kPackTileBytes + (uint32_t)p.meta_rows * p.meta_row_bytes_s +
-                          (p.has_zp ? (uint32_t)p.meta_rows * p.meta_row_bytes_z : 0u);
+      const bool meta = warp == kMetaProducerWarp;
+      const uint32_t tx = meta ? (uint32_t)p.meta_rows * p.meta_row_bytes_s +
+                                     (p.has_zp ? (uint32_t)p.meta_rows * p.meta_row_bytes_z : 0u)
+                               : (uint32_t)kPackTileBytes;
       uint32_t it = 0;
       ItemCursor cur = first_item(p);
       Item item;
@@ -291,27 +304,61 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         for (int ks = item.ks0; ks < item.ks0 + item.count; ++ks, ++it) {
           const int s = it % kStages;
           if (it >= (uint32_t)kStages &&
-              !mbar_wait(bar(BAR_PACK_FREE + s), ((it / kStages) - 1) & 1, abort_flag, 0x110 | s))
+              !mbar_wait(bar(BAR_PACK_FREE + s), ((it / kStages) - 1) & 1, abort_flag, (meta ? 0x120 : 0x110) | s))
             goto w_producer_done;
           const uint32_t fb = bar(BAR_FULL + s);
           mbar_arrive_expect_tx(fb, tx);
           const int k0 = ks * BLOCK_K;
-          tma_load_2d(base + plan.pack + s * kPackTileBytes, &tm_pack, k0, n_tile * (TILE_N / 2), fb);
-          if (COLWISE) {
+          if (!meta) {
+            tma_load_2d(base + plan.pack + s * kPackTileBytes, &tm_pack, k0, n_tile * (TILE_N / 2), fb);
+          } else if (COLWISE) {
             // meta row-major [K/block, N]: box = meta_rows x 128 columns
-            const int mrow = k0 / p.block;
+            const int mrow = k0 >> p.block_shift;
             tma_load_2d(base + plan.scale + s * kScaleTileBytes, &tm_scale, n_tile * TILE_N, mrow, fb);
-            if (p.has_zp)
-              tma_load_2d(base + plan.zp + s * kZpTileBytes, &tm_zp, n_tile * TILE_N, mrow, fb);
+            if (p.has_zp) tma_load_2d(base + plan.zp + s * kZpTileBytes, &tm_zp, n_tile * TILE_N, mrow, fb);
           } else {
             // meta column-major [K, N/block]: box = meta_rows (n blocks) x 64 k
-            const int mrow = n_tile * TILE_N / p.block;
+            const int mrow = (n_tile * TILE_N) >> p.block_shift;
             tma_load_2d(base + plan.scale + s * kScaleTileBytes, &tm_scale, k0, mrow, fb);
             if (p.has_zp) tma_load_2d(base + plan.zp + s * kZpTileBytes, &tm_zp, k0, mrow, fb);
           }
         }
       }
     w_producer_done:;
+    }
+  } else if (DUAL && (warp == 1 || warp == kSecondIssuerWarp)) {
+    // ========================= MMA issuers, DUAL: even steps / odd steps =========================
+    if (lane == 0) {
+      const uint32_t q = warp == 1 ? 0u : 1u;
+      const uint32_t idesc = make_idesc_f16(TILE_N, p.BM);
+      const uint32_t desc_hi = (uint32_t)(make_sw128_kmajor_desc(0) >> 32);
+      const uint32_t desc_lo_flags = (uint32_t)(make_sw128_kmajor_desc(0) & 0xFFFFFFFFu);
+      const uint32_t act_lo0 = desc_lo_flags | (((base + plan.act) >> 4) & 0x3FFFu);
+      const uint32_t act_lo_step = act_stride >> 4;
+      const uint32_t a_tmem0 = tmem_base + (uint32_t)p.a_col0;
+      const uint32_t d_tmem = tmem_base + q * (uint32_t)p.BM;  // one accumulator per issuer, no double buffering
+      uint32_t it = 0, tcount = 0;
+      ItemCursor cur = first_item(p);
+      Item item;
+      for (; next_item(p, cur, item); ++tcount) {
+        if (tcount >= 1u && !mbar_wait(bar(BAR_ACC_EMPTY), (tcount - 1u) & 1u, abort_flag, 0x200 | q)) goto mma2_done;
+        tc_fence_after();
+        uint32_t accumulate = 0u;
+        for (uint32_t st = it + ((it ^ q) & 1u); st < it + (uint32_t)item.count; st += 2) {
+          const uint32_t s = st % kDeqStages, sa = st % kActStages;
+          const uint32_t bar_a = bar(BAR_ACT_FULL) + 8u * sa, bar_d = bar(BAR_DEQ_FULL) + 8u * s;
+          const uint32_t par_sa = (st / kActStages) & 1u, par_s = (st / kDeqStages) & 1u;
+          if (!mbar_try_wait(bar_a, par_sa) && !mbar_wait(bar_a, par_sa, abort_flag, 0x210 | sa)) goto mma2_done;
+          if (!mbar_try_wait(bar_d, par_s) && !mbar_wait(bar_d, par_s, abort_flag, 0x220 | s)) goto mma2_done;
+          tc_fence_after();
+          umma_f16_ts_x4(d_tmem, a_tmem0 + s * kDeqCols, act_lo0 + sa * act_lo_step, desc_hi, idesc, accumulate);
+          accumulate = 1u;
+          umma_commit(bar(BAR_MMA_DONE) + 8u * (st % kDoneBars));
+        }
+        it += (uint32_t)item.count;
+        umma_commit(bar(BAR_ACC_FULL));  // arrives at once for an issuer without a step in this item
+      }
+    mma2_done:;
     }
   } else if (warp == 1) {
     // =============================== MMA issuer =================================
@@ -388,6 +435,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
     uint32_t tcount = 0;
     asm volatile("griddepcontrol.wait;" ::: "memory");  // output and workspace belong to stream order
     const size_t tile_floats = (size_t)p.BM * TILE_N;
+    uint32_t it_base = 0;  // global index of the item's first k step
     ItemCursor cur = first_item(p);
     Item item;
     for (; next_item(p, cur, item); ++tcount) {
@@ -395,6 +443,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       const int ab = tcount % p.acc_bufs;
       if (!mbar_wait(bar(BAR_ACC_FULL + ab), (tcount / p.acc_bufs) & 1, abort_flag, 0x300 | ab)) break;
       tc_fence_after();
+      // DUAL: the item's even steps were summed in accumulator 0 and its odd steps in accumulator 1 (an
+      // item of a single step wrote only one of them); the result is accumulator 0 + accumulator 1.
+      const bool have0 = !DUAL || item.count > 1 || (it_base & 1u) == 0u;
+      const bool have1 = DUAL && (item.count > 1 || (it_base & 1u) == 1u);
+      it_base += (uint32_t)item.count;
+      auto load_acc = [&](int c0, uint32_t (&r)[32]) {
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        if (!DUAL) {
+          tmem_ld_32x32b_x32(lane_base + (uint32_t)(ab * p.BM + c0), r);
+          tmem_ld_wait();
+        } else if (have0 && have1) {
+          uint32_t r1[32];
+          tmem_ld_32x32b_x32(lane_base + (uint32_t)c0, r);
+          tmem_ld_32x32b_x32(lane_base + (uint32_t)(p.BM + c0), r1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r1[j]));
+        } else {
+          tmem_ld_32x32b_x32(lane_base + (uint32_t)((have1 ? p.BM : 0) + c0), r);
+          tmem_ld_wait();
+        }
+      };
       const int n_l = quarter * 32 + lane;
       if (item.role == 1) {
         // ---- a part that hands over: fp32 partial tile [m][n] to the workspace: for a row m
@@ -404,8 +474,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
         const int rows = min(p.BM, p.M - m_tile * p.BM);
         for (int c0 = 0; c0 < rows; c0 += 32) {
           uint32_t r[32];
-          tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(ab * p.BM + c0), r);
-          tmem_ld_wait();
+          load_acc(c0, r);
 #pragma unroll
           for (int j = 0; j < 32; ++j)
             if (c0 + j < rows) dst_ws[(size_t)(c0 + j) * TILE_N] = __uint_as_float(r[j]);
@@ -447,8 +516,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant
       for (int c0 = 0; c0 < p.BM; c0 += 32) {
         if (m0 + c0 >= p.M) break;  // warp-uniform
         uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(ab * p.BM + c0), r);
-        tmem_ld_wait();
+        load_acc(c0, r);
         if (item.role == 2) {
           // add the other parts in part order (a fixed order: the result is reproducible)
           for (int q = 0; q < item.nparts; ++q) {
@@ -626,21 +694,30 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
   p.out = out;
   p.bias = bias;
   // tensor memory: accumulators first, then the dequantized stages
-  p.acc_bufs = (2 * p.BM + kDeqStages * kDeqCols <= 512) ? 2 : 1;
-  p.a_col0 = p.acc_bufs * p.BM;
+  // BM <= 128: two accumulators, one per MMA-issuing thread (DUAL kernels); above, a single accumulator
+  static const bool dual_off = getenv("BLKQ4_TC_NO_DUAL") != nullptr;
+  const bool dual = p.BM <= 128 && !dual_off;
+  p.acc_bufs = dual ? 1 : ((2 * p.BM + kDeqStages * kDeqCols <= 512) ? 2 : 1);
+  p.a_col0 = dual ? 2 * p.BM : p.acc_bufs * p.BM;
   {
     const uint32_t need = (uint32_t)(p.a_col0 + kDeqStages * kDeqCols);
     p.tmem_cols = 32;
     while (p.tmem_cols < need) p.tmem_cols <<= 1;
   }
 
-  // M >= 256: two CTAs per 256 x 256 tile (blkq4_gemm_tc_pair.cuh), each staging half of the activation rows
+  // Two CTAs per 256 (weight columns) x BM tile (blkq4_gemm_tc_pair.cuh), each staging half of the
+  // activation rows; the pair's UMMA N = BM must be a multiple of 32.
   static const bool pair_off = getenv("BLKQ4_TC_NO_PAIR") != nullptr;
-  const bool pair = M >= 256 && !pair_off;
+  static const int pair_min_m = getenv("BLKQ4_TC_PAIR_MIN_M") ? atoi(getenv("BLKQ4_TC_PAIR_MIN_M")) : 256;
+  const bool pair = M >= pair_min_m && !pair_off;
+  if (pair) {
+    p.BM = M >= 256 ? 256 : ((M + 31) / 32) * 32;
+    p.m_tiles = (M + p.BM - 1) / p.BM;
+  }
 
   CUtensorMap tm_act, tm_pack, tm_scale, tm_zp;
   bool ok = encode_tensor_map_2d(&tm_act, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a, (uint64_t)K, (uint64_t)M, BLOCK_K,
-                      pair ? (uint32_t)kPairRows : (uint32_t)p.BM, CU_TENSOR_MAP_SWIZZLE_128B);
+                      pair ? (uint32_t)(p.BM / 2) : (uint32_t)p.BM, CU_TENSOR_MAP_SWIZZLE_128B);
   // No swizzle on the packed tile: the dequantizers' 16-byte loads of eight neighbouring packed
   // columns (64 bytes apart) do conflict four ways, but a 64-byte TMA swizzle that removes the
   // conflicts measured 1-2 % SLOWER on the same GPU (c3 59.2 vs 58.2 us): those loads are not on
@@ -716,10 +793,12 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
   p.ws_flags = reinterpret_cast<unsigned*>(workspace);
   p.ws_partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + sp.flags_bytes);
   const int grid = p.num_items < sms ? p.num_items : sms;
+  // (a 16-stage weight ring measured no faster than 6 with either kernel)
   const SmemPlan plan = make_plan(p.BM, 6, kActStages);
-  auto kern = colwise ? gemm_tc_kernel<true, 6> : gemm_tc_kernel<false, 6>;
-  static std::atomic<int> granted[2][64];
-  cudaError_t e = ensure_dynamic_smem(kern, plan.total, granted[colwise ? 1 : 0]);
+  auto kern = dual ? (colwise ? gemm_tc_kernel<true, 6, true> : gemm_tc_kernel<false, 6, true>)
+                   : (colwise ? gemm_tc_kernel<true, 6, false> : gemm_tc_kernel<false, 6, false>);
+  static std::atomic<int> granted[4][64];
+  cudaError_t e = ensure_dynamic_smem(kern, plan.total, granted[(colwise ? 1 : 0) + (dual ? 2 : 0)]);
   if (e != cudaSuccess) return std::string(cudaGetErrorString(e));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);

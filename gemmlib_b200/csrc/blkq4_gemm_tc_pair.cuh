@@ -24,7 +24,7 @@
 // The loads here carry no cluster multicast: every CTA copies its own rows.  All waits are bounded;
 // the two CTAs meet at a cluster barrier before either frees its tensor memory or exits.
 
-constexpr int kPairRows = 128;  // activation rows staged per CTA = half of the pair's UMMA N
+constexpr int kPairRows = 128;  // most activation rows staged per CTA: half of the pair's UMMA N (p.BM / 2 are used)
 // Rings of the pair kernel.  The activation ring is as deep as the ring of dequantized stages, so
 // that ONE barrier per step ("step full") collects everything the MMAs of the step read - the bytes of
 // both CTAs' activation copies and the arrivals of both CTAs' dequantizer warps - and the MMA thread
@@ -140,6 +140,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
+  const int half = p.BM >> 1;  // activation rows this CTA stages; p.BM (a multiple of 32, <= 256) is the pair's UMMA N
   const int pair = (int)(blockIdx.x >> 1), num_pairs = (int)(gridDim.x >> 1);
   constexpr uint32_t kTmemCols = 512;  // 256 accumulator columns + eight dequantized stages of 32
   constexpr uint32_t kAcol0 = 256;
@@ -148,7 +149,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
   if (threadIdx.x == 0) {
     for (int i = 0; i < kActStages; ++i) mbar_init(bar(BAR_ACT_FULL + i), 1);
     for (int i = 0; i < kStages; ++i) {
-      mbar_init(bar(BAR_FULL + i), 1);
+      mbar_init(bar(BAR_FULL + i), 2);  // packed-tile producer + meta producer
       mbar_init(bar(BAR_PACK_FREE + i), kWarpsPerDeqGroup);
     }
     for (int i = 0; i < kDeqStages; ++i) mbar_init(bar(BAR_DEQ_FULL + i), 1 + 2 * kWarpsPerDeqGroup);  // "step full"
@@ -189,31 +190,34 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
               goto act_producer_done;
           }
           const uint32_t fb = bar(BAR_DEQ_FULL + sa);  // the step's one barrier
-          if (rank == 0) mbar_arrive_expect_tx(fb, 2u * plan.act_bytes);
+          if (rank == 0) mbar_arrive_expect_tx(fb, 2u * (uint32_t)half * 128u);
           tma_load_2d_pair(base + plan.act + sa * act_stride, &tm_act, ks * BLOCK_K,
-                           m_tile * 2 * kPairRows + (int)rank * kPairRows, map_to_cta(fb, 0));
+                           m_tile * p.BM + (int)rank * half, map_to_cta(fb, 0));
         }
       }
     act_producer_done:;
     }
-  } else if (warp == kWeightProducerWarp) {
-    // ==================== TMA producer: this CTA's packed weights and meta =================
+  } else if (warp == kWeightProducerWarp || warp == kMetaProducerWarp) {
+    // ===== TMA producers: this CTA's packed weights (one warp), its scales and zero points (another) =====
     if (lane == 0) {
-      const uint32_t tx = kPackTileBytes + (uint32_t)p.meta_rows * p.meta_row_bytes_s +
-                          (p.has_zp ? (uint32_t)p.meta_rows * p.meta_row_bytes_z : 0u);
+      const bool meta = warp == kMetaProducerWarp;
+      const uint32_t tx = meta ? (uint32_t)p.meta_rows * p.meta_row_bytes_s +
+                                     (p.has_zp ? (uint32_t)p.meta_rows * p.meta_row_bytes_z : 0u)
+                               : (uint32_t)kPackTileBytes;
       uint32_t it = 0;
       for (int item = pair; item < p.num_items; item += num_pairs) {
         const int n_tile = 2 * (item / p.m_tiles) + (int)rank;
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
           const int s = it % kStages;
           if (it >= (uint32_t)kStages &&
-              !mbar_wait(bar(BAR_PACK_FREE + s), ((it / kStages) - 1) & 1, abort_flag, 0x110 | s))
+              !mbar_wait(bar(BAR_PACK_FREE + s), ((it / kStages) - 1) & 1, abort_flag, (meta ? 0x120 : 0x110) | s))
             goto w_producer_done;
           const uint32_t fb = bar(BAR_FULL + s);
           mbar_arrive_expect_tx(fb, tx);
           const int k0 = ks * BLOCK_K;
-          tma_load_2d(base + plan.pack + s * kPackTileBytes, &tm_pack, k0, n_tile * (TILE_N / 2), fb);
-          if (COLWISE) {
+          if (!meta) {
+            tma_load_2d(base + plan.pack + s * kPackTileBytes, &tm_pack, k0, n_tile * (TILE_N / 2), fb);
+          } else if (COLWISE) {
             const int mrow = k0 >> p.block_shift;
             tma_load_2d(base + plan.scale + s * kScaleTileBytes, &tm_scale, n_tile * TILE_N, mrow, fb);
             if (p.has_zp) tma_load_2d(base + plan.zp + s * kZpTileBytes, &tm_zp, n_tile * TILE_N, mrow, fb);
@@ -229,7 +233,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
   } else if (warp == 1) {
     // =============================== MMA issuer: the leader's lane 0 =================================
     if (lane == 0 && rank == 0) {
-      const uint32_t idesc = make_idesc_f16(2 * TILE_N, 2 * kPairRows);
+      const uint32_t idesc = make_idesc_f16(2 * TILE_N, p.BM);
       const uint32_t desc_hi = (uint32_t)(make_sw128_kmajor_desc(0) >> 32);
       const uint32_t desc_lo_flags = (uint32_t)(make_sw128_kmajor_desc(0) & 0xFFFFFFFFu);
       const uint32_t act_lo0 = desc_lo_flags | (((base + plan.act) >> 4) & 0x3FFFu);
@@ -276,8 +280,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
       const int n_tile = 2 * (item / p.m_tiles) + (int)rank, m_tile = item % p.m_tiles;
       if (!mbar_wait_cluster(bar(BAR_ACC_FULL), tcount & 1u, abort_flag, 0x300)) break;
       tc_fence_after();
-      const int m0 = m_tile * 2 * kPairRows;
-      const int rows = min(2 * kPairRows, p.M - m0);
+      const int m0 = m_tile * p.BM;
+      const int rows = min(p.BM, p.M - m0);
       for (int c0 = 0; c0 < rows; c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
