@@ -709,10 +709,18 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
   // activation rows; the pair's UMMA N = BM must be a multiple of 32.
   static const bool pair_off = getenv("BLKQ4_TC_NO_PAIR") != nullptr;
   static const int pair_min_m = getenv("BLKQ4_TC_PAIR_MIN_M") ? atoi(getenv("BLKQ4_TC_PAIR_MIN_M")) : 256;
-  const bool pair = M >= pair_min_m && !pair_off;
+  // ... and only when the pair tiles fill at least one round of the device's pairs: the pair kernel has no
+  // split-K, and e.g. M = 512 on a 4096-wide layer (32 pair tiles) runs faster split over single CTAs.
+  bool pair = M >= pair_min_m && !pair_off;
   if (pair) {
-    p.BM = M >= 256 ? 256 : ((M + 31) / 32) * 32;
-    p.m_tiles = (M + p.BM - 1) / p.BM;
+    const int bm = M >= 256 ? 256 : ((M + 31) / 32) * 32;
+    const int mt = (M + bm - 1) / bm;
+    if (mt * ((p.n_tiles + 1) / 2) < sm_count() / 2) {
+      pair = false;
+    } else {
+      p.BM = bm;
+      p.m_tiles = mt;
+    }
   }
 
   CUtensorMap tm_act, tm_pack, tm_scale, tm_zp;
@@ -753,7 +761,7 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
     cudaError_t e = ensure_dynamic_smem(kern, plan.total, granted[colwise ? 1 : 0]);
     if (e != cudaSuccess) return std::string(cudaGetErrorString(e));
     cudaLaunchConfig_t cfg = {};
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3(kPairThreads);
     cfg.dynamicSmemBytes = plan.total;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
