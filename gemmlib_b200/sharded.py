@@ -4,11 +4,13 @@ The weight [out_features, in_features] is split along out_features (N); rank r o
 rows [r*N/g, (r+1)*N/g), quantizes and prepacks its shard locally, and computes
 ``out_r = input @ W_r^T`` for the replicated input.  The only exchange is an
 all-gather of the outputs along the last dimension at the layer boundary.  On GPUs
-and for M <= 16 on the skinny kernel's fast path that exchange is FUSED into the
-kernel: its epilogue stores the slice into every rank's buffer over NVLink and a
-small second kernel waits for the peers' flags (``PeerGather``, C ABI
-``blkq4_gather_*``).  Everything else all-gathers with ``torch.distributed`` (NCCL on
-GPUs; gloo in the CPU tests of the partitioning logic).  The reference has no
+and for M <= 16 on the skinny kernels' fast paths that exchange is FUSED into the
+kernel (``PeerGather``, C ABI ``blkq4_gather_*``): the decode kernel (M <= 8) stores
+its results into every rank's buffer over NVLink as flagged 8-byte words, waits for
+the peers' words and copies the gathered rows out, all in one launch; for M 9..16 the
+epilogue stores plain fp16 and a small second kernel waits for the peers' flags.
+Everything else all-gathers with ``torch.distributed`` (NCCL on GPUs; gloo in the CPU
+tests of the partitioning logic).  The reference has no
 multi-GPU path; this module is the partition the W4A16 path shards along.
 
 Quantization blocks never straddle a shard when the shard width is a multiple of
