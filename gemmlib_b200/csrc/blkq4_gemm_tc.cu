@@ -671,13 +671,68 @@ SplitPlan plan_split(int M, int N, int K, size_t ws_bytes_available) {
 
 }  // namespace
 
+namespace {
+
+// Plan of the CTA-pair kernel (blkq4_gemm_tc_pair.cuh): two CTAs per 256 (weight columns) x BM tile, each
+// staging half of the activation rows; the pair's UMMA N = BM must be a multiple of 32.  Used for
+// M >= 256 when the pair tiles fill at least one round of the device's pairs (the pair kernel has no
+// split-K: M = 512 on a 4096-wide layer, 32 pair tiles, runs faster split over single CTAs).  With a
+// workspace, and when whole rounds would idle more than a fifth of the pairs' time, the work is cut in
+// balanced ranges.  Measured on B200: 86 pair tiles on 74 pairs (M = 512, 4096 -> 11008) 52 -> 43 us;
+// 112 tiles (M = 256, K = 8192, N = 28672) 103 -> 100 us; 128 tiles (c3, 86 % busy in whole rounds)
+// 57 -> 61 us and 448 tiles (M = 1024) unchanged: one more accumulator hand-over per pair and the fp32
+// exchange of a 128 KB partial tile per CTA cost what the balance gains there.
+struct PairPlan {
+  bool use;
+  int BM, m_tiles, items, balanced;
+  size_t flags_bytes, total_bytes;
+};
+
+PairPlan plan_pair(int M, int N, int K, size_t ws_bytes_available) {
+  static const bool pair_off = getenv("BLKQ4_TC_NO_PAIR") != nullptr;
+  static const int pair_min_m = getenv("BLKQ4_TC_PAIR_MIN_M") ? atoi(getenv("BLKQ4_TC_PAIR_MIN_M")) : 256;
+  static const double balance_below =
+      getenv("BLKQ4_TC_PAIR_BALANCE_BELOW") ? atof(getenv("BLKQ4_TC_PAIR_BALANCE_BELOW")) : 0.80;
+  PairPlan pl{false, 0, 0, 0, 0, 0, 0};
+  if (M < pair_min_m || pair_off) return pl;
+  const int sms = sm_count() > 0 ? sm_count() : 148;
+  const int pairs = sms / 2;
+  pl.BM = M >= 256 ? 256 : ((M + 31) / 32) * 32;
+  pl.m_tiles = (M + pl.BM - 1) / pl.BM;
+  pl.items = pl.m_tiles * (((N + TILE_N - 1) / TILE_N + 1) / 2);
+  if (pl.items < pairs) return pl;
+  pl.use = true;
+  const int k_steps = K / BLOCK_K;
+  const long long total_steps = (long long)pl.items * k_steps;
+  const int rounds = (pl.items + pairs - 1) / pairs;
+  static const bool balance_off = getenv("BLKQ4_TC_NO_BALANCE") != nullptr;
+  if (!balance_off && pl.items > pairs && total_steps < (1ll << 30) / pairs &&
+      total_steps / pairs >= k_steps + 2 * kMinPartSteps && (double)pl.items < balance_below * rounds * pairs) {
+    const size_t flags = ((size_t)sms * sizeof(unsigned) + 255) & ~(size_t)255;
+    const size_t total = flags + (size_t)sms * pl.BM * TILE_N * sizeof(float);
+    if (total <= ws_bytes_available) {
+      pl.balanced = 1;
+      pl.flags_bytes = flags;
+      pl.total_bytes = total;
+    }
+  }
+  return pl;
+}
+
+}  // namespace
+
 size_t gemm_tc_workspace_bytes(int M, int N, int K) {
   if (M <= 16) return 0;
+  const PairPlan pp = plan_pair(M, N, K, ~(size_t)0);
+  if (pp.use) return pp.total_bytes;
   return plan_split(M, N, K, ~(size_t)0).total_bytes;
 }
 
 bool gemm_tc_plan_balanced(int M, int N, int K) {
-  return M > 16 && plan_split(M, N, K, ~(size_t)0).balanced != 0;
+  if (M <= 16) return false;
+  const PairPlan pp = plan_pair(M, N, K, ~(size_t)0);
+  if (pp.use) return pp.balanced != 0;
+  return plan_split(M, N, K, ~(size_t)0).balanced != 0;
 }
 
 std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
@@ -705,22 +760,12 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
     while (p.tmem_cols < need) p.tmem_cols <<= 1;
   }
 
-  // Two CTAs per 256 (weight columns) x BM tile (blkq4_gemm_tc_pair.cuh), each staging half of the
-  // activation rows; the pair's UMMA N = BM must be a multiple of 32.
-  static const bool pair_off = getenv("BLKQ4_TC_NO_PAIR") != nullptr;
-  static const int pair_min_m = getenv("BLKQ4_TC_PAIR_MIN_M") ? atoi(getenv("BLKQ4_TC_PAIR_MIN_M")) : 256;
-  // ... and only when the pair tiles fill at least one round of the device's pairs: the pair kernel has no
-  // split-K, and e.g. M = 512 on a 4096-wide layer (32 pair tiles) runs faster split over single CTAs.
-  bool pair = M >= pair_min_m && !pair_off;
+  const bool ws_ok = workspace && reinterpret_cast<uintptr_t>(workspace) % 256 == 0;
+  const PairPlan pp = plan_pair(M, N, K, ws_ok ? workspace_bytes : 0);
+  const bool pair = pp.use;
   if (pair) {
-    const int bm = M >= 256 ? 256 : ((M + 31) / 32) * 32;
-    const int mt = (M + bm - 1) / bm;
-    if (mt * ((p.n_tiles + 1) / 2) < sm_count() / 2) {
-      pair = false;
-    } else {
-      p.BM = bm;
-      p.m_tiles = mt;
-    }
+    p.BM = pp.BM;
+    p.m_tiles = pp.m_tiles;
   }
 
   CUtensorMap tm_act, tm_pack, tm_scale, tm_zp;
@@ -754,7 +799,11 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
   const int sms = sm_count();
   if (pair) {
     p.k_steps = K / BLOCK_K;
-    p.num_items = p.m_tiles * ((p.n_tiles + 1) / 2);
+    p.num_items = pp.items;
+    p.balanced = pp.balanced;
+    p.total_steps = pp.balanced ? pp.items * p.k_steps : 0;
+    p.ws_flags = reinterpret_cast<unsigned*>(workspace);
+    p.ws_partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + pp.flags_bytes);
     auto kern = colwise ? gemm_tc_pair_kernel<true, kPairWeightStages> : gemm_tc_pair_kernel<false, kPairWeightStages>;
     const SmemPlan plan = make_plan(kPairRows, kPairWeightStages, kPairActStages, kPairOutBytes);
     static std::atomic<int> granted[2][64];
@@ -790,8 +839,7 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
     return std::string();
   }
   const int num_tiles = p.m_tiles * p.n_tiles;
-  const SplitPlan sp = (workspace && reinterpret_cast<uintptr_t>(workspace) % 256 == 0)
-                           ? plan_split(M, N, K, workspace_bytes) : SplitPlan{0, 0, 0, 0};
+  const SplitPlan sp = ws_ok ? plan_split(M, N, K, workspace_bytes) : SplitPlan{0, 0, 0, 0};
   p.split_shift = sp.split_shift;
   p.k_per_item = (K / BLOCK_K) >> sp.split_shift;
   p.num_items = num_tiles << sp.split_shift;

@@ -124,6 +124,46 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
 // warps 0 .. kWeightProducerWarp only: the one-CTA kernel's second issuer and meta producer have no part here
 constexpr int kPairThreads = 32 * (kWeightProducerWarp + 1);
 
+// Work items of one pair.  Whole rounds: pair tiles `pair`, `pair + num_pairs`, ... in full.  Balanced
+// (p.balanced, needs a workspace): the (tile, k step) sequence of the whole problem is cut in one
+// contiguous range per pair (range_bound); a tile that straddles two ranges has its tail computed FIRST
+// by the later pair (role 1: each CTA leaves its fp32 partial tile in the workspace slot of its own
+// CTA index) and its head LAST by the earlier pair (role 2: adds the partial of the CTA two indices up).
+struct PairWalk {
+  int pos, end, step, k_steps, balanced;
+  __device__ __forceinline__ PairWalk(const Params& p, int pair, int num_pairs) {
+    k_steps = p.k_steps;
+    balanced = p.balanced;
+    if (balanced) {
+      pos = range_bound(p.total_steps, k_steps, num_pairs, pair);
+      end = range_bound(p.total_steps, k_steps, num_pairs, pair + 1);
+      step = 0;
+    } else {
+      pos = pair;
+      end = p.num_items;
+      step = num_pairs;
+    }
+  }
+  // role: 0 whole tile, 1 hands a partial tile over, 2 finishes a tile with a partial from the next pair
+  __device__ __forceinline__ bool next(int& tile, int& ks0, int& count, int& role) {
+    if (pos >= end) return false;
+    if (balanced) {
+      tile = pos / k_steps;
+      ks0 = pos - tile * k_steps;
+      count = min(k_steps - ks0, end - pos);
+      role = ks0 > 0 ? 1 : (count < k_steps ? 2 : 0);
+      pos += count;
+    } else {
+      tile = pos;
+      ks0 = 0;
+      count = k_steps;
+      role = 0;
+      pos += step;
+    }
+    return true;
+  }
+};
+
 template <bool COLWISE, int WS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_pack,
@@ -183,9 +223,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
     if (lane == 0) {
       asm volatile("griddepcontrol.wait;" ::: "memory");  // activations belong to stream order
       uint32_t it = 0;
-      for (int item = pair; item < p.num_items; item += num_pairs) {
+      PairWalk walk(p, pair, num_pairs);
+      int item, ks0, count, role;
+      while (walk.next(item, ks0, count, role)) {
         const int m_tile = item % p.m_tiles;
-        for (int ks = 0; ks < k_steps; ++ks, ++it) {
+        for (int ks = ks0; ks < ks0 + count; ++ks, ++it) {
           const int sa = it % kActStages;
           if (it >= (uint32_t)kActStages) {
             const uint32_t g = (it - kActStages) / kCommitSteps;
@@ -207,9 +249,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
       const uint32_t tx = kPackTileBytes + (uint32_t)p.meta_rows * p.meta_row_bytes_s +
                           (p.has_zp ? (uint32_t)p.meta_rows * p.meta_row_bytes_z : 0u);
       uint32_t it = 0;
-      for (int item = pair; item < p.num_items; item += num_pairs) {
+      PairWalk walk(p, pair, num_pairs);
+      int item, ks0, count, role;
+      while (walk.next(item, ks0, count, role)) {
         const int n_tile = 2 * (item / p.m_tiles) + (int)rank;
-        for (int ks = 0; ks < k_steps; ++ks, ++it) {
+        for (int ks = ks0; ks < ks0 + count; ++ks, ++it) {
           const int s = it % kStages;
           if (it >= (uint32_t)kStages &&
               !mbar_wait(bar(BAR_PACK_FREE + s), ((it / kStages) - 1) & 1, abort_flag, 0x110 | s))
@@ -244,24 +288,39 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
       // the barrier of step i + 1 is polled (without blocking) before the MMAs of step i are issued, so
       // that the poll's round trip overlaps the issue
       bool ready = false;
-      for (int item = pair; item < p.num_items; item += num_pairs, ++tcount) {
-        if (tcount >= 1u && !mbar_wait_cluster(bar(BAR_ACC_EMPTY), (tcount - 1u) & 1u, abort_flag, 0x200)) goto mma_done;
-        tc_fence_after();
-        for (int ks = 0; ks < k_steps; ++ks, ++it) {
-          const uint32_t bar_d = bar(BAR_DEQ_FULL) + 8u * s;
-          if (!ready && !mbar_try_wait(bar_d, par_s) && !mbar_wait(bar_d, par_s, abort_flag, 0x220 | s)) goto mma_done;
-          tc_fence_after();
-          const uint32_t a_tmem = a_tmem0 + s * kDeqCols, b_lo = act_lo0 + s * act_lo_step;
-          if (++s == kDeqStages) { s = 0; par_s ^= 1u; }
-          ready = mbar_test_wait(bar(BAR_DEQ_FULL) + 8u * s, par_s);
-          umma_f16_ts_x4_pair(tmem_base, a_tmem, b_lo, desc_hi, idesc, ks > 0 ? 1u : 0u);
-          if (it % kCommitSteps == kCommitSteps - 1) {
-            umma_commit_pair(bar(BAR_MMA_DONE) + 8u * gdone);
-            if (++gdone == kDoneBars) gdone = 0;
-          }
+#define BLKQ4_TC_PAIR_MMA_ITEM(COUNT)                                                                              \
+  {                                                                                                                 \
+    if (tcount >= 1u && !mbar_wait_cluster(bar(BAR_ACC_EMPTY), (tcount - 1u) & 1u, abort_flag, 0x200)) goto mma_done; \
+    tc_fence_after();                                                                                               \
+    for (int ks = 0; ks < (COUNT); ++ks, ++it) {                                                                    \
+      const uint32_t bar_d = bar(BAR_DEQ_FULL) + 8u * s;                                                            \
+      if (!ready && !mbar_try_wait(bar_d, par_s) && !mbar_wait(bar_d, par_s, abort_flag, 0x220 | s)) goto mma_done; \
+      tc_fence_after();                                                                                             \
+      const uint32_t a_tmem = a_tmem0 + s * kDeqCols, b_lo = act_lo0 + s * act_lo_step;                             \
+      if (++s == kDeqStages) { s = 0; par_s ^= 1u; }                                                                \
+      ready = mbar_test_wait(bar(BAR_DEQ_FULL) + 8u * s, par_s);                                                    \
+      umma_f16_ts_x4_pair(tmem_base, a_tmem, b_lo, desc_hi, idesc, ks > 0 ? 1u : 0u);                               \
+      if (it % kCommitSteps == kCommitSteps - 1) {                                                                  \
+        umma_commit_pair(bar(BAR_MMA_DONE) + 8u * gdone);                                                           \
+        if (++gdone == kDoneBars) gdone = 0;                                                                        \
+      }                                                                                                             \
+    }                                                                                                               \
+    umma_commit_pair(bar(BAR_ACC_FULL));                                                                            \
+  }
+      if (!p.balanced) {
+        for (int item = pair; item < p.num_items; item += num_pairs, ++tcount) BLKQ4_TC_PAIR_MMA_ITEM(k_steps)
+      } else {
+        int pos = range_bound(p.total_steps, k_steps, num_pairs, pair);
+        const int end = range_bound(p.total_steps, k_steps, num_pairs, pair + 1);
+        int to_tile_end = k_steps - pos % k_steps;
+        for (; pos < end; ++tcount) {
+          const int count = min(to_tile_end, end - pos);
+          BLKQ4_TC_PAIR_MMA_ITEM(count)
+          pos += count;
+          to_tile_end = k_steps;
         }
-        umma_commit_pair(bar(BAR_ACC_FULL));
       }
+#undef BLKQ4_TC_PAIR_MMA_ITEM
     mma_done:;
     }
   } else if (warp < 2 + kNumEpiWarps) {
@@ -277,16 +336,69 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
     const uint32_t acc_empty_leader = map_to_cta(bar(BAR_ACC_EMPTY), 0);
     uint8_t* stage = base_ptr + plan.out + quarter * (256 * 64);
     const int odd = lane & 1;
-    for (int item = pair; item < p.num_items; item += num_pairs, ++tcount) {
+    const size_t tile_floats = (size_t)p.BM * TILE_N;
+    PairWalk walk(p, pair, num_pairs);
+    int item, ks0, count, role;
+    for (; walk.next(item, ks0, count, role); ++tcount) {
       const int n_tile = 2 * (item / p.m_tiles) + (int)rank, m_tile = item % p.m_tiles;
       if (!mbar_wait_cluster(bar(BAR_ACC_FULL), tcount & 1u, abort_flag, 0x300)) break;
       tc_fence_after();
       const int m0 = m_tile * p.BM;
       const int rows = min(p.BM, p.M - m0);
+      const int n_l = quarter * 32 + lane;
+      if (role == 1) {
+        // ---- the tail of a tile whose head another pair computes: fp32 partial tile [m][n] to this CTA's slot
+        //      of the workspace (for a row m the 32 lanes of a warp write 128 contiguous bytes)
+        float* dst_ws = p.ws_partials + (size_t)blockIdx.x * tile_floats + n_l;
+        for (int c0 = 0; c0 < rows; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (c0 + j < rows) dst_ws[(size_t)(c0 + j) * TILE_N] = __uint_as_float(r[j]);
+        }
+        tc_fence_before();
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) {
+          if (rank == 0) mbar_arrive(bar(BAR_ACC_EMPTY));
+          else mbar_arrive_remote(acc_empty_leader);
+          atomicAdd(p.ws_flags + blockIdx.x, 1u);
+        }
+        continue;
+      }
+      // the CTA of the same rank in the next pair holds the other part of a cut tile
+      const unsigned src_slot = blockIdx.x + 2u;
+      if (role == 2) {
+        if (lane == 0) {
+          const long long t0 = clock64();
+          while (*reinterpret_cast<volatile unsigned*>(p.ws_flags + src_slot) < (unsigned)kNumEpiWarps) {
+            if (*abort_flag || clock64() - t0 > kWaitCycles) {
+              *abort_flag = 1;
+              atomicCAS(&g_gemm_tc_error, 0, 0x320 | quarter);
+              break;
+            }
+          }
+          __threadfence();
+        }
+        __syncwarp();
+        if (*abort_flag) break;
+      }
+      const float* src_ws = p.ws_partials + (size_t)src_slot * tile_floats + n_l;
       for (int c0 = 0; c0 < rows; c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
         tmem_ld_wait();
+        if (role == 2) {
+          // own part + the other pair's part, always in this order: reproducible
+          const float* sq = src_ws + (size_t)c0 * TILE_N;
+          float f[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = (c0 + j < rows) ? __ldcg(sq + (size_t)j * TILE_N) : 0.0f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + f[j]);
+        }
         // lanes pair up (n even / odd): the even lane writes the even rows of the chunk, the odd lane the
         // odd rows, each as half2 (n even, n odd) with its partner's value alongside
         uint8_t* dst = stage + (c0 + odd) * 64 + (lane & ~1) * 2;
@@ -303,6 +415,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
       if (lane == 0) {
         if (rank == 0) mbar_arrive(bar(BAR_ACC_EMPTY));
         else mbar_arrive_remote(acc_empty_leader);
+        // the warp that completes the slot's count (4 writers + 4 readers) puts the flag back to zero
+        if (role == 2 && atomicAdd(p.ws_flags + src_slot, 1u) == (unsigned)(2 * kNumEpiWarps - 1)) p.ws_flags[src_slot] = 0u;
       }
       // staging -> global: one instruction moves four rows' 64-byte pieces
       const int n4 = n_tile * TILE_N + quarter * 32 + (lane & 7) * 4;  // first of this lane's 4 columns
@@ -336,9 +450,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
     const uint32_t nib_shift = (n_l & 8) ? 8u : 0u;
     const uint32_t tmem_row = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) + kAcol0;
     const uint32_t deq_full_leader = map_to_cta(bar(BAR_DEQ_FULL), 0);
-    int my_items = 0;
-    for (int item = pair; item < p.num_items; item += num_pairs) ++my_items;
-    const uint32_t total_its = (uint32_t)my_items * (uint32_t)k_steps;
+    uint32_t total_its = 0;
+    {
+      PairWalk walk(p, pair, num_pairs);
+      int item, ks0, count, role;
+      while (walk.next(item, ks0, count, role)) total_its += (uint32_t)count;
+    }
     for (uint32_t it = group; it < total_its; it += kDeqGroups) {
       const int s = it % kStages, d = it % kDeqStages;
       if (it >= (uint32_t)kDeqStages) {

@@ -1,4 +1,7 @@
-// Skinny W4A16 kernel (M <= 16) for sm_100a: out[M,N] = A[M,K] x dequant(W4[K,N]).
+// Skinny W4A16 kernels (M <= 16) for sm_100a: out[M,N] = A[M,K] x dequant(W4[K,N]).
+// This file holds the dispatch (launch_gemv: decode kernel -> wide kernel, both in files of their
+// own, -> the TMA kernel and the generic kernel below) and the two kernels that take every shape
+// the first two refuse.
 //
 // This regime is bound by HBM bandwidth: every packed weight byte is read once
 // and used for at most 16 outputs, so the kernel is organised around the weight
@@ -270,11 +273,12 @@ gemv_kernel(const __half* __restrict__ a, const uint8_t* __restrict__ packed,
 //
 // Memory side.  Persistent CTAs (one per SM) walk a static list of 16-column tiles.  A
 // producer warp streams the packed weights through a ring of shared-memory slots with TMA
-// (cp.async.bulk.tensor): one unit = 8 packed columns x 256 bytes (4 steps of 64 k, 2 KB)
-// plus the unit's scales / zero points, completing on the slot's "full" mbarrier.  The ring
-// bounds the bytes in flight per SM (~70 KB: enough to cover HBM latency) - measured on B200,
-// asking for a whole launch's bytes up front makes every later small load (activations,
-// scales) queue behind them for microseconds.  Eight consumer warps take units round-robin,
+// (cp.async.bulk.tensor): one unit = 8 packed columns x 512 bytes (kUnitSteps = 8 steps of
+// 64 k, 4 KB) plus the unit's scales / zero points, completing on the slot's "full" mbarrier.
+// The ring (kRing = 32 slots) bounds the bytes in flight per SM (140 KB: enough to cover HBM
+// latency) - measured on B200, asking for a whole launch's bytes up front makes every later
+// small load (activations, scales) queue behind them for microseconds.  kCons = 16 consumer
+// warps take units round-robin,
 // release slots through "empty" mbarriers, and leave their partial sums of a tile in shared
 // memory; the warp that completes a tile adds them in a fixed order, converts and stores.
 //

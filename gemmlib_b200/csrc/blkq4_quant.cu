@@ -1,15 +1,20 @@
 // Fused blockwise 4-bit quantization + prepack for sm_100a.
 //
-// One kernel replaces the reference's three (block_quantize_kernel,
+// One kernel per call replaces the reference's three (block_quantize_kernel,
 // prepack_weights_kernel, prepack_scales_kernel; reference
 // src/mickey/blk_q4/f16_quant_sm80.cuh:593-653) and its three temporary device
 // buffers (src/blkq4_f16_gemm_sm80.cu:282-290).  It is memory bound: every fp16
-// weight is read from HBM once (16-byte loads along K), staged in shared memory,
-// and the packed bytes, scales and zero points are written once in their final
-// order.  Output bytes are bit-identical to the reference's.
+// weight is read from HBM once (16-byte loads along K) and the packed bytes, scales
+// and zero points are written once in their final order.  Output bytes are
+// bit-identical to the reference's.  Two kernels:
 //
-// A CTA owns a TK x TN tile of the K x N weight.  Phases, separated by
-// __syncthreads():
+// quant_prepack_colwise_kernel<BLOCK> - column-wise blocks with 16-byte aligned rows
+// (the benchmark configurations): one thread per 16-byte packed chunk (16 k of the
+// columns n0 and n0 + 8), everything in registers, the block's range by shuffles over
+// the BLOCK / 16 neighbouring lanes, no shared memory.
+//
+// quant_prepack_kernel<BLOCK, COLWISE> - row-wise blocks and unaligned inputs: a CTA
+// owns a TK x TN tile of the K x N weight.  Phases, separated by __syncthreads():
 //   1. load the tile into shared memory
 //   2. min/max of every 16-element segment of a quantization block
 //   3. combine segments per block -> fp16 scale, zero point, fp32 reciprocal

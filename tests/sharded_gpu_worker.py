@@ -47,6 +47,21 @@ def main():
             torch.cuda.synchronize()
             ok &= bool((out.float() - want).abs().max() <= tol)
         del graph
+    # unfused paths (M > 16: kernel + NCCL all-gather): the caller's buffer receives the result too
+    x = torch.randn(40, K, generator=g).half().to(dev)
+    full_layer = BlkQ4Linear(64, True, True, w)
+    want = full_layer(x).float()
+    tol = 2.0 ** -8 * max(1.0, float(want.abs().max()))
+    sharded = ShardedBlkQ4Linear(64, True, True, w, peer_gather=pg)
+    out = torch.full((40, N), float("nan"), dtype=torch.float16, device=dev)
+    ret = sharded(x, out=out)
+    torch.cuda.synchronize()
+    ok &= ret.data_ptr() == out.data_ptr() and bool((out.float() - want).abs().max() <= tol)
+    local_only = ShardedBlkQ4Linear(64, True, True, w, gather_output=False)
+    part = torch.full((40, N // world), float("nan"), dtype=torch.float16, device=dev)
+    local_only(x, out=part)
+    torch.cuda.synchronize()
+    ok &= bool((part.float() - want[:, rank * (N // world):(rank + 1) * (N // world)]).abs().max() <= tol)
     ok &= pg.status() == 0
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)

@@ -197,7 +197,8 @@ def test_split_k_with_workspace(case):
 
 
 @pytest.mark.parametrize("case", [(64, True, True, 48, 28672, 1024), (128, True, False, 300, 11008, 4096),
-                                  (32, False, True, 100, 22528, 4096)],
+                                  (32, False, True, 100, 22528, 4096), (64, True, True, 512, 11008, 4096),
+                                  (32, False, False, 257, 28672, 2048)],
                          ids=lambda c: "-".join(map(str, c)))
 def test_balanced_ranges_with_workspace(case):
     """More output tiles than SMs, but far from a whole number of rounds: with a workspace every CTA
@@ -209,8 +210,12 @@ def test_balanced_ranges_with_workspace(case):
     block, colwise, has_zp, M, N, K = case
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     tiles = -(-M // min(256, -(-M // 16) * 16)) * -(-N // 128)
-    if not (tiles > sms and tiles < 0.8 * -(-tiles // sms) * sms and tiles * (K // 64) // sms >= K // 64 + 8):
-        pytest.skip(f"{tiles} tiles on {sms} SMs: not a balanced plan on this device")
+    units = sms
+    if M >= 256 and -(-M // 256) * -(-(-(-N // 128)) // 2) >= sms // 2:
+        # the CTA-pair kernel: 256-column pair tiles on sms / 2 pairs
+        tiles, units = -(-M // 256) * -(-(-(-N // 128)) // 2), sms // 2
+    if not (tiles > units and tiles < 0.8 * -(-tiles // units) * units and tiles * (K // 64) // units >= K // 64 + 8):
+        pytest.skip(f"{tiles} tiles on {units} units: not a balanced plan on this device")
     need = capi.gemm_workspace_size(M, N, K)
     assert need > 4 * sms
     ws = torch.zeros(need, dtype=torch.uint8, device="cuda")
@@ -231,10 +236,10 @@ def test_balanced_ranges_with_workspace(case):
 def test_workspace_plans():
     from gemmlib_b200 import capi
 
-    assert capi.gemm_workspace_size(2048, 4096, 4096) == 0   # 256 tiles on 148 SMs: 86 % busy, left alone
+    assert capi.gemm_workspace_size(2048, 4096, 4096) == 0   # 128 pair tiles on 74 CTA pairs: 86 % busy, left alone
     assert capi.gemm_workspace_size(16, 4096, 4096) == 0     # skinny kernel
-    assert capi.gemm_workspace_size(512, 4096, 4096) > 0     # 64 tiles: split-K
-    assert capi.gemm_workspace_size(512, 11008, 4096) > 0    # 172 tiles: balanced ranges
+    assert capi.gemm_workspace_size(512, 4096, 4096) > 0     # 64 tiles: split-K over single CTAs
+    assert capi.gemm_workspace_size(512, 11008, 4096) > 0    # 86 pair tiles: balanced ranges
 
 
 def test_config_c1_cpu_reference_case():
