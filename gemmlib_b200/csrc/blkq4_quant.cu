@@ -85,6 +85,26 @@ __device__ __forceinline__ uint32_t quantize_one(float v, float r, float zp) {
   return (uint32_t)__float2int_rz(__fadd_rz(x, 0.5f));
 }
 
+// quantize_one for two values at once (sm_100a packed fp32 arithmetic).
+__device__ __forceinline__ unsigned long long pack_f32x2(float x, float y) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(x), "f"(y));
+  return r;
+}
+__device__ __forceinline__ void quantize_two(float2 v, unsigned long long r2, unsigned long long zp2, uint32_t& q0,
+                                             uint32_t& q1) {
+  unsigned long long x;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(x) : "l"(pack_f32x2(v.x, v.y)), "l"(r2), "l"(zp2));
+  asm("add.rz.f32x2 %0, %1, %2;" : "=l"(x) : "l"(x), "l"(pack_f32x2(0.5f, 0.5f)));
+  float a, b;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(x));
+  uint32_t ua, ub;
+  asm("cvt.rzi.u32.f32 %0, %1;" : "=r"(ua) : "f"(a));  // negative -> 0
+  asm("cvt.rzi.u32.f32 %0, %1;" : "=r"(ub) : "f"(b));
+  q0 = min(ua, 15u);
+  q1 = min(ub, 15u);
+}
+
 template <int BLOCK, bool COLWISE>
 __global__ void __launch_bounds__(kThreads)
 quant_prepack_kernel(const __half* __restrict__ w, int K, int N, int ld, bool vec_ok,
@@ -344,11 +364,18 @@ quant_prepack_colwise_kernel(const __half* __restrict__ w, int K, int N, int ld,
   const float rb = (sb != 0.0f) ? __fdiv_rn(1.0f, sb) : 0.0f;
   const float za = (float)zpa, zb = (float)zpb;
 
+  // Two values per instruction (fma.rn.f32x2 / add.rz.f32x2 are the same IEEE operations as the
+  // scalar ones in quantize_one); the clamp moves behind the conversion: trunc(x + 0.5) saturated
+  // at 0 by the conversion to unsigned, then min(., 15) - the same integer for every non-NaN x.
   uint32_t qa[16], qb[16];
+  const unsigned long long ra2 = pack_f32x2(ra, ra), za2 = pack_f32x2(za, za);
+  const unsigned long long rb2 = pack_f32x2(rb, rb), zb2 = pack_f32x2(zb, zb);
+  const __half2* ha2 = reinterpret_cast<const __half2*>(va);
+  const __half2* hb2 = reinterpret_cast<const __half2*>(vb);
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    qa[i] = quantize_one(__half2float(ha[i]), ra, za);
-    qb[i] = quantize_one(__half2float(hb[i]), rb, zb);
+  for (int i = 0; i < 8; ++i) {
+    quantize_two(__half22float2(ha2[i]), ra2, za2, qa[2 * i], qa[2 * i + 1]);
+    quantize_two(__half22float2(hb2[i]), rb2, zb2, qb[2 * i], qb[2 * i + 1]);
   }
   // Byte 4 row + sub = q[2 row + (sub >> 1), sub & 1 ? nb : na] | q[the same k + 8, same n] << 4
   // (reference dev_prepack_weights, f16_quant_sm80.cuh:362-417).
