@@ -356,8 +356,10 @@ std::string launch_gemv_wide(int block, bool colwise, int M, int N, int K, cudaS
   // Long K only: every CTA first reduces the whole activation matrix to its per-step correction
   // terms, and that prologue pays off over many tiles of long columns.  Measured on B200 against the
   // generic skinny kernel: K = 8192, N = 28672 symmetric, M = 16: 73 vs 79 us, M = 9: 60 vs 72 us;
-  // K = 4096, N = 11008 with zero points, M = 16: 25 vs 21 us (so those stay on the generic kernel).
-  if (K < 8192) return kStreamUnsupported;
+  // K = 4096, N = 11008 with zero points, M = 16: 25 vs 21 us; K = 8192, N = 14336 (a half-width shard,
+  // three tiles per CTA), M = 16: 56 vs 46 us.  So: long K and at least four tiles per resident CTA;
+  // everything else stays on the TMA kernel.
+  if (K < 8192 || N / (16 * NT) < 8 * sm_count()) return kStreamUnsupported;
   if (!colwise || block < 64 || M < 9 || M > 16 || K % group_k != 0 || K / group_k < kWarps || N % (16 * NT) != 0 ||
       reinterpret_cast<uintptr_t>(scales) % 16 != 0 || (zp && reinterpret_cast<uintptr_t>(zp) % 16 != 0))
     return kStreamUnsupported;
