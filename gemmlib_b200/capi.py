@@ -35,6 +35,7 @@ SYMBOLS = (
     "blkq4_gather_status",
     "blkq4_gather_destroy",
     "blkq4_gather_reset",
+    "blkq4_gather_supported_sm100",
     "blkq4_reset",
     "blkq4_version",
 )
@@ -79,6 +80,8 @@ def _load() -> ctypes.CDLL:
     lib.blkq4_last_kernel_status.restype = i
     lib.blkq4_gather_reset.argtypes = [vp]
     lib.blkq4_gather_reset.restype = i
+    lib.blkq4_gather_supported_sm100.argtypes = [i, ctypes.c_bool, i, i, i]
+    lib.blkq4_gather_supported_sm100.restype = i
     lib.blkq4_reset.argtypes = [vp]
     lib.blkq4_reset.restype = i
     lib.blkq4_gather_create.argtypes = [i, i, sz, ctypes.POINTER(vp), vp, vp]
@@ -164,6 +167,12 @@ EARLY_WEIGHT_FETCH = 1  # BLKQ4_GEMM_EARLY_WEIGHT_FETCH
 def gemm_workspace_size(m: int, n: int, k: int) -> int:
     """Bytes of zeroed workspace with which the tensor-core kernel would split K (0: it would not)."""
     return int(lib.blkq4_gemm_workspace_size(m, n, k))
+
+
+def gather_supported(block_size: int, col_wise: bool, m: int, n_shard: int, k: int) -> bool:
+    """Whether GatherContext.gemm takes the shape (fused GEMM + all-gather), else the caller computes
+    locally and all-gathers with its own collective."""
+    return bool(lib.blkq4_gather_supported_sm100(block_size, col_wise, m, n_shard, k))
 
 
 def static_scratch_size() -> int:

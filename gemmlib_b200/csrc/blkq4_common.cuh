@@ -79,7 +79,9 @@ std::string launch_gemv_gather(int block, bool colwise, int M, int N, int K, cud
 std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
                            const __half* a, const uint8_t* packed, const __half* scales,
                            const uint8_t* zp, __half* out, const __half* bias, void* workspace,
-                           size_t workspace_bytes, unsigned flags);
+                           size_t workspace_bytes, unsigned flags, const GatherTable* gt = nullptr);
+// True when launch_gemm_tc takes the problem with a GatherTable (the CTA-pair kernel's fused all-gather).
+bool gemm_tc_gather_supported(int M, int N, int K);
 // Bytes of zero-initialised workspace with which launch_gemm_tc would split K for this problem
 // (0: it would not).
 size_t gemm_tc_workspace_bytes(int M, int N, int K);

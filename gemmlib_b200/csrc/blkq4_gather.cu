@@ -59,6 +59,7 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
 // CTA here has passed launch_dependents).
 __global__ void __launch_bounds__(256)
 gather_wait_copy_kernel(uint8_t* local, int world, unsigned long long buf_bytes, uint4* out, unsigned long long n16) {
+  // out == nullptr: wait only (a large result is copied out by gather_copy_kernel afterwards)
   __shared__ unsigned s_epoch;
   if (threadIdx.x == 0)
     s_epoch = atomicAdd(reinterpret_cast<unsigned*>(local + kGatherTicketOff), 1u) / kGatherWaitCtas + 1u;
@@ -79,6 +80,19 @@ gather_wait_copy_kernel(uint8_t* local, int world, unsigned long long buf_bytes,
   }
   __syncthreads();
   // Peers wrote these lines through NVLink into this GPU's memory: read around L1.
+  if (!out) return;
+  const uint4* src = reinterpret_cast<const uint4*>(local + kGatherCtrlBytes + (size_t)slot * buf_bytes);
+  for (unsigned long long i = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; i < n16;
+       i += (unsigned long long)gridDim.x * blockDim.x)
+    out[i] = __ldcg(src + i);
+}
+
+// Copy-out of a large gathered result (the tensor-core path): runs after the wait kernel has
+// completed, when this rank's epoch word holds the call's epoch, so the buffer's parity is read
+// from the device and the launch replays from a CUDA graph.
+__global__ void __launch_bounds__(256)
+gather_copy_kernel(const uint8_t* local, unsigned long long buf_bytes, uint4* out, unsigned long long n16) {
+  const unsigned slot = *reinterpret_cast<const volatile unsigned*>(local + kGatherEpochOff) & 1u;
   const uint4* src = reinterpret_cast<const uint4*>(local + kGatherCtrlBytes + (size_t)slot * buf_bytes);
   for (unsigned long long i = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; i < n16;
        i += (unsigned long long)gridDim.x * blockDim.x)
@@ -191,6 +205,35 @@ extern "C" int blkq4_fp16_gemm_gather_sm100(void* ctx, int block_size, bool colu
   gt.n_total = (int)n_total;
   gt.buf_bytes = c->buf_bytes;
   auto stream = reinterpret_cast<cudaStream_t>(stream_ptr);
+  if (m > 16) {
+    // Tensor-core path: the CTA-pair kernel stores its tiles into every rank's gathered buffer and
+    // publishes like the skinny kernels; the wait kernel only waits, a full-width kernel copies out.
+    if (reinterpret_cast<uintptr_t>(scales_ptr) % 16 != 0 ||
+        (has_offsets && reinterpret_cast<uintptr_t>(offsets_ptr) % 16 != 0))
+      return blkq4::fail(err, "Kernel execution failed: Error Misaligned Operand (scales and offsets must be 16-byte aligned for m > 16)");
+    const std::string e2 = blkq4::launch_gemm_tc(
+        block_size, column_wise_blocking, m, n_shard, k, stream, reinterpret_cast<const __half*>(act_ptr),
+        reinterpret_cast<const uint8_t*>(weights_ptr), reinterpret_cast<const __half*>(scales_ptr),
+        has_offsets ? reinterpret_cast<const uint8_t*>(offsets_ptr) : nullptr, nullptr, nullptr, nullptr, 0, flags, &gt);
+    if (!e2.empty()) return blkq4::fail(err, "Kernel execution failed: " + e2);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blkq4::kGatherWaitCtas);
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, blkq4::gather_wait_copy_kernel, c->base[c->rank], c->world,
+                       (unsigned long long)c->buf_bytes, (uint4*)nullptr, 0ull);
+    const int sms = blkq4::sm_count() > 0 ? blkq4::sm_count() : 148;
+    blkq4::gather_copy_kernel<<<2 * sms, 256, 0, stream>>>(c->base[c->rank], (unsigned long long)c->buf_bytes,
+                                                           reinterpret_cast<uint4*>(output_ptr), output_size / 16);
+    const cudaError_t ce = cudaGetLastError();
+    if (ce != cudaSuccess) return blkq4::fail(err, std::string("Kernel execution failed: ") + cudaGetErrorString(ce));
+    return 0;
+  }
   bool delivered = false;
   const std::string e = blkq4::launch_gemv_gather(
       block_size, column_wise_blocking, m, n_shard, k, stream, reinterpret_cast<const __half*>(act_ptr),
@@ -214,6 +257,14 @@ extern "C" int blkq4_fp16_gemm_gather_sm100(void* ctx, int block_size, bool colu
   const cudaError_t ce = cudaGetLastError();
   if (ce != cudaSuccess) return blkq4::fail(err, std::string("Kernel execution failed: ") + cudaGetErrorString(ce));
   return 0;
+}
+
+extern "C" int blkq4_gather_supported_sm100(int block_size, bool column_wise_blocking, int m, int n_shard, int k) {
+  if (!blkq4::supported_block(block_size) || m <= 0 || n_shard <= 0 || k <= 0) return 0;
+  const blkq4::Blocking b(block_size, column_wise_blocking);
+  if ((k % 64) != 0 || (k % b.bk) != 0 || (n_shard % 16) != 0 || (n_shard % b.bn) != 0) return 0;
+  if (m <= 16) return (column_wise_blocking && block_size >= 64 && k >= 512 && k <= 32768) ? 1 : 0;
+  return blkq4::gemm_tc_gather_supported(m, n_shard, k) ? 1 : 0;
 }
 
 extern "C" int blkq4_gather_status(void* ctx, void* stream_ptr) {

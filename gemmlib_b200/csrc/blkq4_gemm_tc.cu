@@ -102,6 +102,7 @@ struct Params {
   int k_steps;         // K / 64
   int total_steps;     // tiles * k_steps
   float* ws_partials;  // balanced: [cta][BM][128] fp32; otherwise [tile][split-1][BM][128]
+  GatherTable gt;      // pair kernel, gt.world > 0: the result goes to every rank's gathered buffer instead of `out`
   unsigned* ws_flags;  // balanced: [cta]; otherwise [tile]: arrivals (self-resetting)
 };
 
@@ -728,6 +729,10 @@ size_t gemm_tc_workspace_bytes(int M, int N, int K) {
   return plan_split(M, N, K, ~(size_t)0).total_bytes;
 }
 
+bool gemm_tc_gather_supported(int M, int N, int K) {
+  return M > 16 && plan_pair(M, N, K, 0).use;
+}
+
 bool gemm_tc_plan_balanced(int M, int N, int K) {
   if (M <= 16) return false;
   const PairPlan pp = plan_pair(M, N, K, ~(size_t)0);
@@ -738,8 +743,9 @@ bool gemm_tc_plan_balanced(int M, int N, int K) {
 std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStream_t stream,
                            const __half* a, const uint8_t* packed, const __half* scales,
                            const uint8_t* zp, __half* out, const __half* bias, void* workspace,
-                           size_t workspace_bytes, unsigned flags) {
+                           size_t workspace_bytes, unsigned flags, const GatherTable* gt) {
   Params p{};
+  if (gt) p.gt = *gt;
   p.M = M; p.N = N; p.K = K; p.block = block;
   p.block_shift = block == 16 ? 4 : block == 32 ? 5 : block == 64 ? 6 : 7;
   p.BM = M >= 256 ? 256 : ((M + 15) / 16) * 16;
@@ -761,8 +767,10 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
   }
 
   const bool ws_ok = workspace && reinterpret_cast<uintptr_t>(workspace) % 256 == 0;
-  const PairPlan pp = plan_pair(M, N, K, ws_ok ? workspace_bytes : 0);
+  // the fused exchange lives in the pair kernel's epilogue and runs in whole rounds
+  const PairPlan pp = plan_pair(M, N, K, (ws_ok && !gt) ? workspace_bytes : 0);
   const bool pair = pp.use;
+  if (gt && !pair) return "unsupported shape for the fused all-gather";
   if (pair) {
     p.BM = pp.BM;
     p.m_tiles = pp.m_tiles;

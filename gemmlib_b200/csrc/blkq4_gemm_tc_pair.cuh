@@ -179,6 +179,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
   const uint32_t bars = base + plan.bars;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + plan.bars + BAR_COUNT * 8);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + plan.bars + BAR_COUNT * 8 + 8);
+  unsigned* s_done = reinterpret_cast<unsigned*>(base_ptr + plan.bars + BAR_COUNT * 8 + 12);  // epilogue warps done storing
   auto bar = [&](int id) { return bars + 8u * (uint32_t)id; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -202,6 +203,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
       mbar_init(bar(BAR_ACC_EMPTY + i), 2 * kNumEpiWarps);
     }
     *abort_flag = 0;
+    *s_done = 0u;
     mbar_init_fence();
   }
   if (warp == 1) {
@@ -334,6 +336,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
     uint32_t tcount = 0;
     asm volatile("griddepcontrol.wait;" ::: "memory");  // the output belongs to stream order
     const uint32_t acc_empty_leader = map_to_cta(bar(BAR_ACC_EMPTY), 0);
+    // Fused all-gather: the call's epoch is one past the calls completed so far (the word only changes
+    // when every CTA of this call has finished); even / odd epochs alternate between two buffers.
+    unsigned gather_epoch = 0;
+    size_t gather_off = 0;
+    if (p.gt.world > 0) {
+      gather_epoch = *reinterpret_cast<volatile unsigned*>(p.gt.base[p.gt.rank] + kGatherEpochOff) + 1u;
+      gather_off = kGatherCtrlBytes + (size_t)(gather_epoch & 1u) * p.gt.buf_bytes;
+    }
     uint8_t* stage = base_ptr + plan.out + quarter * (256 * 64);
     const int odd = lane & 1;
     const size_t tile_floats = (size_t)p.BM * TILE_N;
@@ -427,19 +437,55 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
         b01 = *reinterpret_cast<const __half2*>(p.bias + n4);
         b23 = *reinterpret_cast<const __half2*>(p.bias + n4 + 2);
       }
-      __half* gdst = p.out + (size_t)(m0 + (lane >> 3)) * p.N + n4;
-      for (int r0 = 0; r0 < rows; r0 += 4) {
-        uint2 v = *reinterpret_cast<const uint2*>(stage + r0 * 64 + lane * 8);
-        if (add_bias) {
-          // the bias is added to the ROUNDED result in fp16, as a separate `output += bias` would
-          __half2 lo = __hadd2(*reinterpret_cast<__half2*>(&v.x), b01), hi = __hadd2(*reinterpret_cast<__half2*>(&v.y), b23);
-          v.x = *reinterpret_cast<uint32_t*>(&lo);
-          v.y = *reinterpret_cast<uint32_t*>(&hi);
+      if (p.gt.world == 0) {
+        __half* gdst = p.out + (size_t)(m0 + (lane >> 3)) * p.N + n4;
+        for (int r0 = 0; r0 < rows; r0 += 4) {
+          uint2 v = *reinterpret_cast<const uint2*>(stage + r0 * 64 + lane * 8);
+          if (add_bias) {
+            // the bias is added to the ROUNDED result in fp16, as a separate `output += bias` would
+            __half2 lo = __hadd2(*reinterpret_cast<__half2*>(&v.x), b01), hi = __hadd2(*reinterpret_cast<__half2*>(&v.y), b23);
+            v.x = *reinterpret_cast<uint32_t*>(&lo);
+            v.y = *reinterpret_cast<uint32_t*>(&hi);
+          }
+          if (n_ok && r0 + (lane >> 3) < rows) *reinterpret_cast<uint2*>(gdst) = v;
+          gdst += 4 * (size_t)p.N;
         }
-        if (n_ok && r0 + (lane >> 3) < rows) *reinterpret_cast<uint2*>(gdst) = v;
-        gdst += 4 * (size_t)p.N;
+      } else {
+        // Fused all-gather: this rank's columns go straight into EVERY rank's gathered buffer
+        // [M, n_total] (plain stores over NVLink for the peers), under the next tile's MMAs.
+        const size_t row_bytes = (size_t)p.gt.n_total * 2;
+        const size_t off0 = gather_off + (size_t)(m0 + (lane >> 3)) * row_bytes + ((size_t)p.gt.rank * p.N + n4) * 2;
+        for (int r0 = 0; r0 < rows; r0 += 4) {
+          const uint2 v = *reinterpret_cast<const uint2*>(stage + r0 * 64 + lane * 8);
+          if (n_ok && r0 + (lane >> 3) < rows) {
+            const size_t off = off0 + (size_t)r0 * row_bytes;
+            for (int r = 0; r < p.gt.world; ++r) *reinterpret_cast<uint2*>(p.gt.base[r] + off) = v;
+          }
+        }
       }
       __syncwarp();  // the block is rewritten by the next tile
+    }
+    if (p.gt.world > 0 && !*abort_flag) {
+      // Publish (the chain of the skinny kernels' exchange): storing lanes -> lane 0 of their warp,
+      // warps -> the CTA's last epilogue warp (fence + shared counter), CTAs -> the grid's last CTA
+      // (system fence + counter in this rank's block), which advances the local epoch and raises this
+      // rank's flag in every rank's block.  One system-scope fence per CTA.
+      __syncwarp();
+      if (lane == 0) __threadfence_block();
+      if (lane == 0 && atomicAdd(s_done, 1u) == (unsigned)kNumEpiWarps - 1u) {
+        uint8_t* local = p.gt.base[p.gt.rank];
+        __threadfence_system();
+        const unsigned arrived = atomicAdd(reinterpret_cast<unsigned*>(local + kGatherDoneOff), 1u);
+        if (arrived == gridDim.x - 1) {
+          __threadfence_system();
+          *reinterpret_cast<volatile unsigned*>(local + kGatherDoneOff) = 0u;
+          *reinterpret_cast<volatile unsigned*>(local + kGatherEpochOff) = gather_epoch;
+          __threadfence_system();
+          const size_t foff = kGatherFlagsOff + ((gather_epoch & 1u) * kGatherMaxRanks + p.gt.rank) * sizeof(unsigned);
+          for (int r = 0; r < p.gt.world; ++r)
+            *reinterpret_cast<volatile unsigned*>(p.gt.base[r] + foff) = gather_epoch;
+        }
+      }
     }
   } else if (warp < kWeightProducerWarp) {
     // =============================== dequantizers: this CTA's 128 weight columns ===============================

@@ -95,10 +95,13 @@ class PeerGather:
             raise error
 
     def supports(self, layer, rows: int) -> bool:
-        """Shapes the fused kernel takes (the library refuses the others)."""
-        return (rows <= min(16, self.max_rows) and layer.col_wise and layer.block_size >= 64
-                and 512 <= layer.in_features <= 32768
-                and layer.out_features * self.world == self.out_features)
+        """Shapes the fused kernels take (the library refuses the others): decode and skinny shapes
+        up to 16 rows, and prefill shapes on the CTA-pair tensor-core kernel."""
+        from . import capi
+
+        if rows > self.max_rows or layer.out_features * self.world != self.out_features:
+            return False
+        return capi.gather_supported(layer.block_size, layer.col_wise, rows, layer.out_features, layer.in_features)
 
     def forward(self, layer, x, out_full, flags=0):
         """``out_full[M, N] = x[M, K] @ W^T`` with this rank computing its ``layer``'s columns."""

@@ -47,6 +47,24 @@ def main():
             torch.cuda.synchronize()
             ok &= bool((out.float() - want).abs().max() <= tol)
         del graph
+    # prefill on the CTA-pair kernel: its epilogue stores straight into every rank's exchange buffer
+    Mp, Kp = 512, 1024
+    Np = 256 * 40 * world                      # 80 pair tiles per rank: at least one round of 74 pairs
+    wp = (torch.randn(Np, Kp, generator=g) * 0.02).half().to(dev)
+    xp = torch.randn(Mp, Kp, generator=g).half().to(dev)
+    pgp = PeerGather(Mp, Np)
+    full_p = BlkQ4Linear(64, True, False, wp)
+    want_p = full_p(xp).float()
+    tol_p = 2.0 ** -8 * max(1.0, float(want_p.abs().max()))
+    sharded_p = ShardedBlkQ4Linear(64, True, False, wp, peer_gather=pgp)
+    ok &= pgp.supports(sharded_p.local, Mp)
+    for it in range(4):
+        got = sharded_p(xp)
+        torch.cuda.synchronize()
+        ok &= bool((got.float() - want_p).abs().max() <= tol_p)
+    ok &= pgp.status() == 0
+    dist.barrier()
+    pgp.close()
     # unfused paths (M > 16: kernel + NCCL all-gather): the caller's buffer receives the result too
     x = torch.randn(40, K, generator=g).half().to(dev)
     full_layer = BlkQ4Linear(64, True, True, w)

@@ -53,6 +53,56 @@ def test_world_size_one_fused_gather_matches_plain(M, has_zp, block):
     pg.close()
 
 
+@pytest.mark.parametrize("M,has_zp,block,colwise", [(300, True, 64, True), (512, False, 32, False)])
+def test_world_size_one_fused_gather_on_the_tensor_core_path(M, has_zp, block, colwise):
+    """Prefill shapes: the CTA-pair GEMM kernel stores its tiles into the exchange buffer and publishes,
+    the wait kernel waits, the copy kernel copies out.  World size 1 exercises the whole protocol - both
+    buffer parities, a moving epoch, CUDA-graph replay - and the result must be the plain kernel's, bit
+    for bit (same kernel, same tiles; only the destination differs)."""
+    from gemmlib_b200 import capi
+    from gemmlib_b200.ms_blkq4linear import BlkQ4Linear
+    from gemmlib_b200.sharded import PeerGather
+
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    K = 1024
+    N = 256 * -(-(sms // 2) // -(-M // 256))     # enough 256-column pair tiles for one round of the SM pairs
+    layer = BlkQ4Linear(block, colwise, not has_zp, gaussian_weight(N, K, seed=5).cuda())
+    x = gaussian_act(M, K, seed=6).cuda()
+    want = torch.empty(M, N, dtype=torch.float16, device="cuda")
+    capi.gemm(block, colwise, M, N, K, x, layer.q_weights, layer.q_scales, layer.q_zp if has_zp else None, want)
+    pg = PeerGather(M, N)
+    assert pg.supports(layer, M)
+    assert not pg.supports(layer, 64)            # between the skinny and the pair kernel: not fused
+    outs = []
+    for _ in range(3):
+        full = torch.zeros(M, N, dtype=torch.float16, device="cuda")
+        pg.forward(layer, x, full)
+        outs.append(full)
+    full_g = torch.zeros(M, N, dtype=torch.float16, device="cuda")
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=s):
+        pg.forward(layer, x, full_g)
+    for _ in range(3):
+        full_g.zero_()
+        g.replay()
+    torch.cuda.synchronize()
+    assert pg.status() == 0 and capi.last_kernel_status() == 0
+    for full in outs + [full_g]:
+        assert torch.equal(full.view(torch.int16), want.view(torch.int16))
+    # a skinny call on the same context afterwards: the protocols share epochs and tickets
+    x1 = gaussian_act(1, K, seed=7).cuda()
+    one = torch.zeros(1, N, dtype=torch.float16, device="cuda")
+    if pg.supports(layer, 1):
+        pg.forward(layer, x1, one)
+        torch.cuda.synchronize()
+        assert pg.status() == 0
+        ref1 = layer(x1)
+        assert torch.allclose(one.float(), ref1.float(), rtol=0, atol=2.0 ** -8 * max(1.0, float(ref1.abs().max())))
+    pg.close()
+
+
 def test_unsupported_shape_is_refused_not_miscomputed():
     from gemmlib_b200 import capi
     from gemmlib_b200.ms_blkq4linear import BlkQ4Linear
