@@ -787,8 +787,10 @@ NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction per GPU on this
 def bench_c4_sharded(torch, dist, dev, peaks, world, rank, peer_factory):
     """configs[3] sharded: K=8192, N=28672 split along N over the ranks (block 128, symmetric), every
     rank ends with the full [M, N].  Per M: the local shard alone ("compute") and the whole layer
-    ("end_to_end": fused kernel + exchange for M <= 16, tensor-core kernel + NCCL all-gather above),
-    with the bound max(HBM time, tensor time, NVLink time of (g-1)/g * 2MN bytes into each GPU)."""
+    ("end_to_end": the fused kernel + exchange where the library takes the shape - skinny kernels up to
+    M = 16, the CTA-pair tensor-core kernel for prefill shapes - else kernel + NCCL all-gather; for M > 16
+    the NCCL variant is timed beside the fused one), with the bound max(HBM time, tensor time, NVLink
+    time of (g-1)/g * 2MN bytes into each GPU)."""
     from gemmlib_b200.ms_blkq4linear import BlkQ4Linear
     from gemmlib_b200.sharded import gather_columns
 
@@ -799,7 +801,7 @@ def bench_c4_sharded(torch, dist, dev, peaks, world, rank, peer_factory):
     gen = torch.Generator(device=dev).manual_seed(70 + rank)
     layers = [BlkQ4Linear(block, True, True, (torch.randn(ns, K, generator=gen, device=dev) * 0.015).to(torch.float16))
               for _ in range(nsets)]
-    peer = peer_factory(16, N)
+    peer = peer_factory(4096, N)
     stream = torch.cuda.Stream()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     rows = []
@@ -836,25 +838,35 @@ def bench_c4_sharded(torch, dist, dev, peaks, world, rank, peer_factory):
             for lyr in use:
                 lyr(x, out=shard_out)
 
+        fused = peer is not None and peer.supports(use[0], M)
+
         def e2e():
             for lyr in use:
-                if M <= 16 and peer is not None:
+                if fused:
                     peer.forward(lyr, x, full, flags=1)
                 else:
                     gather_columns(lyr(x, out=shard_out))
 
+        def e2e_nccl():
+            for lyr in use:
+                gather_columns(lyr(x, out=shard_out))
+
         scale = nsets / len(use)
         us_c = timed(compute, reps) * scale
         us_e = timed(e2e, reps) * scale
+        us_n = timed(e2e_nccl, reps) * scale if (fused and M > 16) else None
         nbytes = algorithmic_bytes(M, K, ns, block, True, False)
         flops = 2.0 * M * ns * K
         t_hbm, t_tc = nbytes / (peaks["hbm_gbs"] * 1e3), flops / (peaks["tflops"] * 1e6)
         t_link = (world - 1) / world * 2.0 * M * N / (NVLINK_GBS * 1e3)
         bound = max(t_hbm, t_tc, t_link)
-        rows.append({"M": M, "compute_us": round(us_c, 2), "end_to_end_us": round(us_e, 2),
-                     "bound_us": round(bound, 2), "bound": "hbm" if bound == t_hbm else ("tensor" if bound == t_tc else "nvlink"),
-                     "compute_frac": round(max(t_hbm, t_tc) / us_c, 4), "end_to_end_frac": round(bound / us_e, 4),
-                     "exchange": "fused in the kernel" if (M <= 16 and peer is not None) else "NCCL all-gather"})
+        row = {"M": M, "compute_us": round(us_c, 2), "end_to_end_us": round(us_e, 2),
+               "bound_us": round(bound, 2), "bound": "hbm" if bound == t_hbm else ("tensor" if bound == t_tc else "nvlink"),
+               "compute_frac": round(max(t_hbm, t_tc) / us_c, 4), "end_to_end_frac": round(bound / us_e, 4),
+               "exchange": "fused in the kernel" if fused else "NCCL all-gather"}
+        if us_n is not None:
+            row["end_to_end_nccl_us"] = round(us_n, 2)
+        rows.append(row)
     if peer is not None:
         torch.cuda.synchronize()
         dist.barrier()
