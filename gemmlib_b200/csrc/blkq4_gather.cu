@@ -1,13 +1,19 @@
-// Fused skinny GEMM + all-gather for N-sharded layers on one box (one process per GPU).
+// Fused GEMM + all-gather for N-sharded layers on one box (one process per GPU).
 //
-// Each rank owns one device block (control words, per-source flags, two gathered buffers) that
-// all peers map through CUDA IPC.  A layer call is two launches on the caller's stream:
-//   1. the skinny kernel, whose epilogue stores this rank's [M, N/g] columns straight into
-//      EVERY rank's gathered buffer over NVLink (plain peer stores; no multicast, no pulls) and
-//      whose last CTA raises this rank's flag in every rank's block;
-//   2. a small kernel, resident alongside the first, that waits - bounded - until the flags of
-//      all ranks carry the call's epoch, then copies the complete [M, N] result into the
-//      caller's output tensor.
+// Each rank owns one device block (control words, per-source flags, two gathered fp16 buffers, two
+// buffers of flagged words) that all peers map through CUDA IPC.  Three shapes of a layer call, all
+// on the caller's stream:
+//   decode kernel (M <= 8), ONE launch: the kernel stores its results into every rank's block as
+//      8-byte words {two fp16, epoch} (the data is its own flag), then polls its own block -
+//      bounded - until every word carries the call's epoch and copies the result out;
+//   TMA skinny kernel (M <= 16), TWO launches: the epilogue stores this rank's [M, N/g] columns
+//      straight into EVERY rank's gathered buffer over NVLink (plain peer stores; no multicast, no
+//      pulls) and the grid's last CTA raises this rank's flag in every rank's block; a small kernel,
+//      resident alongside the first, waits - bounded - until the flags of all ranks carry the call's
+//      epoch, then copies the complete [M, N] result into the caller's output tensor;
+//   CTA-pair tensor-core kernel (prefill), THREE launches: the GEMM's epilogue stores every output
+//      tile into every rank's gathered buffer under the MMAs of the next tile and publishes like
+//      the skinny kernel; the small kernel only waits; a full-width kernel copies out.
 // Everything a launch needs to know about "which call is this" lives in device memory (the
 // epoch word), so the pair can be captured in a CUDA graph and replayed.
 //
