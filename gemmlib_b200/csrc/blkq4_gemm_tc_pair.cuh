@@ -180,6 +180,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + plan.bars + BAR_COUNT * 8);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + plan.bars + BAR_COUNT * 8 + 8);
   unsigned* s_done = reinterpret_cast<unsigned*>(base_ptr + plan.bars + BAR_COUNT * 8 + 12);  // epilogue warps done storing
+  unsigned* s_epi = reinterpret_cast<unsigned*>(base_ptr + plan.bars + BAR_COUNT * 8 + 16);   // epilogue warps' barrier count
+  static_assert(BAR_COUNT * 8 + 20 <= 512, "barrier block too small");
   auto bar = [&](int id) { return bars + 8u * (uint32_t)id; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -204,6 +206,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
     }
     *abort_flag = 0;
     *s_done = 0u;
+    *s_epi = 0u;
     mbar_init_fence();
   }
   if (warp == 1) {
@@ -345,6 +348,28 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
       gather_off = kGatherCtrlBytes + (size_t)(gather_epoch & 1u) * p.gt.buf_bytes;
     }
     uint8_t* stage = base_ptr + plan.out + quarter * (256 * 64);
+    // Barrier of the four epilogue warps (gather mode), bounded like every wait here: a counter in
+    // shared memory that only grows; a warp that sees the CTA's abort flag leaves instead of waiting.
+    unsigned epi_calls = 0;
+    auto epi_barrier = [&]() -> bool {
+      __syncwarp();
+      ++epi_calls;
+      if (lane == 0) {
+        __threadfence_block();
+        atomicAdd(s_epi, 1u);
+        const long long t0 = clock64();
+        while (*reinterpret_cast<volatile unsigned*>(s_epi) < epi_calls * (unsigned)kNumEpiWarps) {
+          if (*abort_flag || clock64() - t0 > kWaitCycles) {
+            *abort_flag = 1;
+            atomicCAS(&g_gemm_tc_error, 0, 0x330 | quarter);
+            break;
+          }
+        }
+        __threadfence_block();
+      }
+      __syncwarp();
+      return *abort_flag == 0;
+    };
     const int odd = lane & 1;
     const size_t tile_floats = (size_t)p.BM * TILE_N;
     PairWalk walk(p, pair, num_pairs);
@@ -452,16 +477,27 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
         }
       } else {
         // Fused all-gather: this rank's columns go straight into EVERY rank's gathered buffer
-        // [M, n_total] (plain stores over NVLink for the peers), under the next tile's MMAs.
+        // [M, n_total] (plain stores over NVLink for the peers), under the next tile's MMAs.  Peer
+        // stores want long contiguous runs, so here the four warps wait for one another and every warp
+        // then writes whole 256-byte rows of the CTA's 128 columns (16 bytes per lane, two rows per
+        // instruction) instead of its own 64-byte pieces (measured at 4 ranks: 64-byte pieces held the
+        // kernel at twice its compute time).
+        if (!epi_barrier()) break;
+        const uint8_t* stage_all = base_ptr + plan.out;
+        const int c8 = (lane & 15) * 8;                               // first of this lane's 8 columns in the tile
+        const bool n_ok8 = n_tile * TILE_N + c8 + 7 < p.N;            // N is a multiple of 16
         const size_t row_bytes = (size_t)p.gt.n_total * 2;
-        const size_t off0 = gather_off + (size_t)(m0 + (lane >> 3)) * row_bytes + ((size_t)p.gt.rank * p.N + n4) * 2;
-        for (int r0 = 0; r0 < rows; r0 += 4) {
-          const uint2 v = *reinterpret_cast<const uint2*>(stage + r0 * 64 + lane * 8);
-          if (n_ok && r0 + (lane >> 3) < rows) {
-            const size_t off = off0 + (size_t)r0 * row_bytes;
-            for (int r = 0; r < p.gt.world; ++r) *reinterpret_cast<uint2*>(p.gt.base[r] + off) = v;
+        const size_t off0 = gather_off + ((size_t)p.gt.rank * p.N + (size_t)n_tile * TILE_N + c8) * 2;
+        const uint8_t* src0 = stage_all + (c8 >> 5) * (256 * 64) + (c8 & 31) * 2;
+        for (int r0 = 2 * quarter; r0 < rows; r0 += 2 * kNumEpiWarps) {
+          const int row = r0 + (lane >> 4);
+          if (n_ok8 && row < rows) {
+            const uint4 v = *reinterpret_cast<const uint4*>(src0 + row * 64);
+            const size_t off = off0 + (size_t)(m0 + row) * row_bytes;
+            for (int r = 0; r < p.gt.world; ++r) *reinterpret_cast<uint4*>(p.gt.base[r] + off) = v;
           }
         }
+        if (!epi_barrier()) break;  // the staging blocks are rewritten by the next tile
       }
       __syncwarp();  // the block is rewritten by the next tile
     }
