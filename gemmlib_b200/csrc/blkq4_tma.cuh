@@ -126,6 +126,21 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait that may stay suspended for up to `ns` nanoseconds before it reports "not yet": a waiting
+// role then polls once per microsecond instead of spinning, and leaves the issue slots and the ALU
+// pipe to the warps that compute (measured on the tensor-core kernel at M = 64: ~40 % of all issued
+// instructions were polls).
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait: gives up after `max_cycles`, or as soon as another thread of the CTA has
 // given up (abort_flag, in shared memory).  On expiry records `who` in *error_word (global)
 // and returns false; the caller drains instead of hanging the GPU.
@@ -134,7 +149,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_hint(bar, parity, 1000u)) return true;
     if (*abort_flag) return false;
     if (clock64() - t0 > max_cycles) {
       *abort_flag = 1;
