@@ -58,6 +58,7 @@ int sm_count();
 constexpr int kGatherMaxRanks = 8;
 constexpr int kGatherCtrlBytes = 1024;
 constexpr int kGatherEpochOff = 0, kGatherDoneOff = 4, kGatherErrorOff = 8, kGatherTicketOff = 12, kGatherFlagsOff = 64;
+constexpr int kGatherMaxPrefillRanks = 4;  // the tensor-core path's fused exchange (see blkq4_fp16_gemm_gather_sm100)
 constexpr int kGatherWaitCtas = 8;  // fixed grid of the wait kernel: its call number is tickets / 8
 
 struct GatherTable {

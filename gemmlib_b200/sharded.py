@@ -101,6 +101,8 @@ class PeerGather:
 
         if rows > self.max_rows or layer.out_features * self.world != self.out_features:
             return False
+        if rows > 16 and self.world > 4:
+            return False  # the prefill path's peer stores do not scale to eight destinations (measured)
         return capi.gather_supported(layer.block_size, layer.col_wise, rows, layer.out_features, layer.in_features)
 
     def forward(self, layer, x, out_full, flags=0):

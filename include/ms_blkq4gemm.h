@@ -205,7 +205,7 @@ int blkq4_fp16_gemm_static_ws_sm100(
  * copies the result out.  Other shapes on the skinny kernel's TMA path (m <= 16, 512 <= K <= 32768)
  * take two launches: the kernel stores fp16 results and raises a per-rank flag, a second small
  * kernel waits for all flags and copies out.  Prefill shapes on the CTA-pair tensor-core kernel
- * (m >= 256 with at least one round of 256 x 256 tiles per pair of SMs) take three launches: the
+ * (m >= 256 with at least one round of 256 x 256 tiles per pair of SMs, at most 4 ranks) take three launches: the
  * GEMM kernel's epilogue stores every output tile into all ranks' exchange buffers, under the MMAs
  * of the next tile, and raises the per-rank flag; the small kernel waits; a full-width kernel
  * copies out.  All ranks must make the same sequence of calls;
@@ -213,7 +213,7 @@ int blkq4_fp16_gemm_static_ws_sm100(
  * outside these paths is refused with an error text starting "Kernel execution failed: unsupported":
  * compute with blkq4_fp16_gemm_sm80 and all-gather with the caller's collective instead;
  * blkq4_gather_supported_sm100 answers the question beforehand (1 / 0; a pure function of its
- * arguments and of the device's SM count).  blkq4_gather_status synchronises `stream` and returns 0, or
+ * arguments and of the device's SM count; for m > 16 the context's world size must also be <= 4).  blkq4_gather_status synchronises `stream` and returns 0, or
  * (0x400 | rank) of the first rank whose data did not arrive in time; blkq4_gather_reset
  * (device drained on every rank, between the same two calls on every rank) clears that state.
  * blkq4_gather_destroy frees the rank's block: peers store into it from their own kernels, so
