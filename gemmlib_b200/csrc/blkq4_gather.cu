@@ -24,6 +24,7 @@
 // The reference has no multi-GPU path; this file has no counterpart there.
 #include <cstddef>
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -218,7 +219,8 @@ extern "C" int blkq4_fp16_gemm_gather_sm100(void* ctx, int block_size, bool colu
     // against 1402 us for kernel + NCCL all-gather at 2 ranks and 722 against 992 us at 4, but
     // 2130 against 826 us at 8 - plain peer stores to seven destinations at once collapse to
     // ~100 GB/s per rank - so eight ranks are sent back to the caller's collective.
-    if (c->world > blkq4::kGatherMaxPrefillRanks)
+    static const int max_prefill_ranks = getenv("BLKQ4_GATHER_PREFILL_MAX_RANKS") ? atoi(getenv("BLKQ4_GATHER_PREFILL_MAX_RANKS")) : blkq4::kGatherMaxPrefillRanks;
+    if (c->world > max_prefill_ranks)
       return blkq4::fail(err, "Kernel execution failed: unsupported world size for the fused all-gather of m > 16");
     if (reinterpret_cast<uintptr_t>(scales_ptr) % 16 != 0 ||
         (has_offsets && reinterpret_cast<uintptr_t>(offsets_ptr) % 16 != 0))

@@ -494,7 +494,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
           if (n_ok8 && row < rows) {
             const uint4 v = *reinterpret_cast<const uint4*>(src0 + row * 64);
             const size_t off = off0 + (size_t)(m0 + row) * row_bytes;
-            for (int r = 0; r < p.gt.world; ++r) *reinterpret_cast<uint4*>(p.gt.base[r] + off) = v;
+            // destinations in rotated order, starting after this rank: at any moment the ranks of a job
+            // aim at different peers instead of all at the same one
+            int r = p.gt.rank;
+            for (int i = 0; i < p.gt.world; ++i) {
+              r = r + 1 == p.gt.world ? 0 : r + 1;
+              *reinterpret_cast<uint4*>(p.gt.base[r] + off) = v;
+            }
           }
         }
         if (!epi_barrier()) break;  // the staging blocks are rewritten by the next tile

@@ -19,6 +19,8 @@ bytes of the corresponding slice of the full quantized weight.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 from torch import nn
@@ -101,7 +103,7 @@ class PeerGather:
 
         if rows > self.max_rows or layer.out_features * self.world != self.out_features:
             return False
-        if rows > 16 and self.world > 4:
+        if rows > 16 and self.world > int(os.environ.get("BLKQ4_GATHER_PREFILL_MAX_RANKS", "4")):
             return False  # the prefill path's peer stores do not scale to eight destinations (measured)
         return capi.gather_supported(layer.block_size, layer.col_wise, rows, layer.out_features, layer.in_features)
 
