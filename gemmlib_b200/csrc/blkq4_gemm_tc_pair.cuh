@@ -231,7 +231,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
       PairWalk walk(p, pair, num_pairs);
       int item, ks0, count, role;
       while (walk.next(item, ks0, count, role)) {
-        const int m_tile = item % p.m_tiles;
+        const int m_tile = p.n_fastest ? item / p.n_pairs : item % p.m_tiles;
         for (int ks = ks0; ks < ks0 + count; ++ks, ++it) {
           const int sa = it % kActStages;
           if (it >= (uint32_t)kActStages) {
@@ -257,7 +257,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
       PairWalk walk(p, pair, num_pairs);
       int item, ks0, count, role;
       while (walk.next(item, ks0, count, role)) {
-        const int n_tile = 2 * (item / p.m_tiles) + (int)rank;
+        const int n_tile = 2 * (p.n_fastest ? item % p.n_pairs : item / p.m_tiles) + (int)rank;
         for (int ks = ks0; ks < ks0 + count; ++ks, ++it) {
           const int s = it % kStages;
           if (it >= (uint32_t)kStages &&
@@ -375,7 +375,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
     PairWalk walk(p, pair, num_pairs);
     int item, ks0, count, role;
     for (; walk.next(item, ks0, count, role); ++tcount) {
-      const int n_tile = 2 * (item / p.m_tiles) + (int)rank, m_tile = item % p.m_tiles;
+      const int n_tile = 2 * (p.n_fastest ? item % p.n_pairs : item / p.m_tiles) + (int)rank;
+      const int m_tile = p.n_fastest ? item / p.n_pairs : item % p.m_tiles;
       if (!mbar_wait_cluster(bar(BAR_ACC_FULL), tcount & 1u, abort_flag, 0x300)) break;
       tc_fence_after();
       const int m0 = m_tile * p.BM;
