@@ -256,6 +256,10 @@ extern "C" int blkq4_fp16_gemm_gather_sm100(void* ctx, int block_size, bool colu
   if (!e.empty()) return blkq4::fail(err, "Kernel execution failed: " + e);
   if (delivered) return 0;  // one launch did everything
   const unsigned long long n16 = output_size / 16;
+  // The wait kernel's eight CTAs copy 32 KB per round trip to L2: fine for a few rows, ~1 us per 32 KB
+  // beyond that (M = 16 of a 28672-wide layer: 0.9 MB, ~28 us).  Larger results are copied out by a
+  // full-width kernel after the wait, like the tensor-core path's.
+  const bool big = output_size > (size_t)128 * 1024;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(blkq4::kGatherWaitCtas);
   cfg.blockDim = dim3(256);
@@ -266,7 +270,15 @@ extern "C" int blkq4_fp16_gemm_gather_sm100(void* ctx, int block_size, bool colu
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cudaLaunchKernelEx(&cfg, blkq4::gather_wait_copy_kernel, c->base[c->rank], c->world,
-                     (unsigned long long)c->buf_bytes, reinterpret_cast<uint4*>(output_ptr), n16);
+                     (unsigned long long)c->buf_bytes, big ? (uint4*)nullptr : reinterpret_cast<uint4*>(output_ptr),
+                     big ? 0ull : n16);
+  if (big) {
+    const int sms = blkq4::sm_count() > 0 ? blkq4::sm_count() : 148;
+    const unsigned long long want = (n16 + 255) / 256;
+    const unsigned grid = (unsigned)(want < (unsigned long long)(2 * sms) ? want : (unsigned long long)(2 * sms));
+    blkq4::gather_copy_kernel<<<grid, 256, 0, stream>>>(c->base[c->rank], (unsigned long long)c->buf_bytes,
+                                                        reinterpret_cast<uint4*>(output_ptr), n16);
+  }
   const cudaError_t ce = cudaGetLastError();
   if (ce != cudaSuccess) return blkq4::fail(err, std::string("Kernel execution failed: ") + cudaGetErrorString(ce));
   return 0;

@@ -20,12 +20,15 @@ pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
 
 
-@pytest.mark.parametrize("M,has_zp,block", [(1, False, 64), (4, True, 64), (7, True, 128), (8, False, 64), (16, False, 128)])
-def test_world_size_one_fused_gather_matches_plain(M, has_zp, block):
+@pytest.mark.parametrize("M,has_zp,block,N", [(1, False, 64, 1536), (4, True, 64, 1536), (7, True, 128, 1536),
+                                              (8, False, 64, 1536), (16, False, 128, 1536),
+                                              (16, True, 64, 8192),    # 256 KB result: copied out by the full-width kernel
+                                              (12, False, 64, 6144)])
+def test_world_size_one_fused_gather_matches_plain(M, has_zp, block, N):
     from gemmlib_b200.ms_blkq4linear import BlkQ4Linear
     from gemmlib_b200.sharded import PeerGather
 
-    K, N = 2048, 1536
+    K = 2048
     layer = BlkQ4Linear(block, True, not has_zp, gaussian_weight(N, K, seed=5).cuda())
     x = gaussian_act(M, K, seed=6).cuda()
     want = layer(x)
