@@ -216,8 +216,9 @@ extern "C" int blkq4_fp16_gemm_gather_sm100(void* ctx, int block_size, bool colu
     // Tensor-core path: the CTA-pair kernel stores its tiles into every rank's gathered buffer and
     // publishes like the skinny kernels; the wait kernel only waits, a full-width kernel copies out.
     // Up to four ranks by default: measured on B200 (K = 8192, N = 28672, M = 4096) the fused call takes
-    // 907 us against 1402 us for kernel + NCCL all-gather at 2 ranks, 717 against 992 us at 4, and 857
-    // against 826 us at 8 - the peer stores run at ~275 GB/s per GPU whatever the number of ranks.
+    // 862-888 us against 1300-1404 us for kernel + NCCL all-gather at 2 ranks, 717 against 992 us at 4, and
+    // 778 against 817 us at 8 - every GPU takes in ~300 GB/s from its peers whatever their number, about what
+    // NCCL's all-gather reaches on the same box, so at 8 ranks the exchange, not the GEMM, sets the time.
     static const int max_prefill_ranks = getenv("BLKQ4_GATHER_PREFILL_MAX_RANKS") ? atoi(getenv("BLKQ4_GATHER_PREFILL_MAX_RANKS")) : blkq4::kGatherMaxPrefillRanks;
     if (c->world > max_prefill_ranks)
       return blkq4::fail(err, "Kernel execution failed: unsupported world size for the fused all-gather of m > 16");

@@ -102,6 +102,7 @@ struct Params {
   int k_steps;         // K / 64
   int total_steps;     // tiles * k_steps
   float* ws_partials;  // balanced: [cta][BM][128] fp32; otherwise [tile][split-1][BM][128]
+  int gather_bulk;         // pair kernel, gather mode: peer copies as cp.async.bulk of whole rows
   int n_fastest, n_pairs;  // pair kernel: tile order (0: the m tiles of a pair of weight columns run together; 1: the column pairs of an m tile)
   GatherTable gt;      // pair kernel, gt.world > 0: the result goes to every rank's gathered buffer instead of `out`
   unsigned* ws_flags;  // balanced: [cta]; otherwise [tile]: arrivals (self-resetting)
@@ -814,6 +815,8 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
     // ranks fall into a few hundred rows of every destination
     static const bool nf_off = getenv("BLKQ4_TC_GATHER_M_FASTEST") != nullptr;
     p.n_fastest = (gt && !nf_off) ? 1 : 0;
+    static const bool bulk_off = getenv("BLKQ4_TC_GATHER_NO_BULK") != nullptr;
+    p.gather_bulk = (gt && !bulk_off) ? 1 : 0;
     p.balanced = pp.balanced;
     p.total_steps = pp.balanced ? pp.items * p.k_steps : 0;
     p.ws_flags = reinterpret_cast<unsigned*>(workspace);
