@@ -23,6 +23,12 @@
 //   FULL / PACK_FREE (weight ring) stay local to each CTA.
 // The loads here carry no cluster multicast: every CTA copies its own rows.  All waits are bounded;
 // the two CTAs meet at a cluster barrier before either frees its tensor memory or exits.
+//
+// Work distribution: whole tiles in rounds over the resident pairs, or (with a workspace) one balanced
+// range of k steps per pair with cut tiles finished through fp32 partial tiles (PairWalk).
+// Epilogue: tensor memory -> fp16 staging in shared memory -> accumulator released -> global memory
+// under the next tile's MMAs; with a GatherTable (N-sharded layers) the last hop goes to EVERY rank's
+// exchange buffer as bulk copies of whole rows, and the grid's last CTA raises this rank's flag there.
 
 constexpr int kPairRows = 128;  // most activation rows staged per CTA: half of the pair's UMMA N (p.BM / 2 are used)
 // Rings of the pair kernel.  The activation ring is as deep as the ring of dequantized stages, so
