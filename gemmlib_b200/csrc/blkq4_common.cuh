@@ -89,6 +89,9 @@ size_t gemm_tc_workspace_bytes(int M, int N, int K);
 // True when the preferred plan of the problem is the balanced one (more tiles than SMs): its workspace
 // only buys balance; without it the same kernel runs in whole rounds.
 bool gemm_tc_plan_balanced(int M, int N, int K);
+// True when the one-CTA kernel's split-K plan of the problem needs more than `capacity` bytes (the
+// static-scratch entry point refuses exactly those problems).
+bool gemm_tc_split_plan_refusable(int M, int N, int K, size_t capacity);
 
 // Synchronises `stream` and returns the tensor-core kernel's device error word
 // (0 = every bounded wait completed; -1 = the stream itself reported an error).

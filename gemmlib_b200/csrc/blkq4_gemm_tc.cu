@@ -703,21 +703,25 @@ PairPlan plan_pair(int M, int N, int K, size_t ws_bytes_available) {
   pl.BM = M >= 256 ? 256 : ((M + 31) / 32) * 32;
   pl.m_tiles = (M + pl.BM - 1) / pl.BM;
   pl.items = pl.m_tiles * (((N + TILE_N - 1) / TILE_N + 1) / 2);
-  if (pl.items < pairs) return pl;
-  pl.use = true;
   const int k_steps = K / BLOCK_K;
   const long long total_steps = (long long)pl.items * k_steps;
   const int rounds = (pl.items + pairs - 1) / pairs;
   static const bool balance_off = getenv("BLKQ4_TC_NO_BALANCE") != nullptr;
-  if (!balance_off && pl.items > pairs && total_steps < (1ll << 30) / pairs &&
-      total_steps / pairs >= k_steps + 2 * kMinPartSteps && (double)pl.items < balance_below * rounds * pairs) {
-    const size_t flags = ((size_t)sms * sizeof(unsigned) + 255) & ~(size_t)255;
-    const size_t total = flags + (size_t)sms * pl.BM * TILE_N * sizeof(float);
-    if (total <= ws_bytes_available) {
-      pl.balanced = 1;
-      pl.flags_bytes = flags;
-      pl.total_bytes = total;
-    }
+  // Fewer tiles than pairs: the one-CTA kernel splits K.  (The pair kernel can do it too - ranges shorter
+  // than a tile, a tile finished from several partial tiles - but measured slower: M = 512, K = N = 4096
+  // 35.8 vs 28.7 us, K = 11008 54.0 vs 48.6 us; a 128 KB fp32 partial tile per CTA is a dear exchange.)
+  if (pl.items < pairs) return pl;
+  // Balanced ranges need a workspace (one flag word and one fp32 partial tile per CTA), ranges of at least
+  // eight steps, and pay when whole rounds would idle more than a fifth of the pairs' time.
+  const size_t flags = ((size_t)sms * sizeof(unsigned) + 255) & ~(size_t)255;
+  const size_t total = flags + (size_t)sms * pl.BM * TILE_N * sizeof(float);
+  const bool can_balance = !balance_off && total_steps < (1ll << 30) / pairs && total_steps / pairs >= 8 &&
+                           (double)pl.items < balance_below * rounds * pairs && total <= ws_bytes_available;
+  pl.use = true;
+  if (can_balance) {
+    pl.balanced = 1;
+    pl.flags_bytes = flags;
+    pl.total_bytes = total;
   }
   return pl;
 }
@@ -729,6 +733,12 @@ size_t gemm_tc_workspace_bytes(int M, int N, int K) {
   const PairPlan pp = plan_pair(M, N, K, ~(size_t)0);
   if (pp.use) return pp.total_bytes;
   return plan_split(M, N, K, ~(size_t)0).total_bytes;
+}
+
+bool gemm_tc_split_plan_refusable(int M, int N, int K, size_t capacity) {
+  if (M <= 16) return false;
+  const SplitPlan sp = plan_split(M, N, K, ~(size_t)0);
+  return sp.total_bytes > capacity && sp.balanced == 0;
 }
 
 bool gemm_tc_gather_supported(int M, int N, int K) {
@@ -849,7 +859,8 @@ std::string launch_gemm_tc(int block, bool colwise, int M, int N, int K, cudaStr
       if (dev >= 0 && dev < 64) max_pairs[colwise ? 1 : 0][dev].store(pairs, std::memory_order_relaxed);
     }
     cfg.numAttrs = (flags & BLKQ4_GEMM_EARLY_WEIGHT_FETCH) ? 1 : 0;
-    cfg.gridDim = dim3(2 * (p.num_items < pairs ? p.num_items : pairs));
+    // balanced ranges use every resident pair, whole rounds at most one pair per tile
+    cfg.gridDim = dim3(2 * ((p.balanced || p.num_items >= pairs) ? pairs : p.num_items));
     e = cudaLaunchKernelEx(&cfg, kern, tm_act, tm_pack, tm_scale, tm_zp, p);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return std::string(cudaGetErrorString(e));

@@ -411,16 +411,27 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
         }
         continue;
       }
-      // the CTA of the same rank in the next pair holds the other part of a cut tile
+      // The other parts of a cut tile belong to the CTAs of the same rank in the following pairs: every
+      // pair whose (non-empty) range starts before the tile ends.  Ranges shorter than a tile give a tile
+      // several such parts (the split-K of problems with fewer tiles than pairs).
       const unsigned src_slot = blockIdx.x + 2u;
+      int nparts = 0;
       if (role == 2) {
+        const int tile_end = (item + 1) * k_steps;
+        for (int q = pair + 1; q < num_pairs; ++q) {
+          const int qs = range_bound(p.total_steps, k_steps, num_pairs, q);
+          if (qs >= tile_end) break;
+          if (range_bound(p.total_steps, k_steps, num_pairs, q + 1) > qs) ++nparts; else break;
+        }
         if (lane == 0) {
           const long long t0 = clock64();
-          while (*reinterpret_cast<volatile unsigned*>(p.ws_flags + src_slot) < (unsigned)kNumEpiWarps) {
-            if (*abort_flag || clock64() - t0 > kWaitCycles) {
-              *abort_flag = 1;
-              atomicCAS(&g_gemm_tc_error, 0, 0x320 | quarter);
-              break;
+          for (int i = 0; i < nparts; ++i) {
+            while (*reinterpret_cast<volatile unsigned*>(p.ws_flags + src_slot + 2u * i) < (unsigned)kNumEpiWarps) {
+              if (*abort_flag || clock64() - t0 > kWaitCycles) {
+                *abort_flag = 1;
+                atomicCAS(&g_gemm_tc_error, 0, 0x320 | quarter);
+                break;
+              }
             }
           }
           __threadfence();
@@ -433,9 +444,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
         tmem_ld_wait();
-        if (role == 2) {
-          // own part + the other pair's part, always in this order: reproducible
-          const float* sq = src_ws + (size_t)c0 * TILE_N;
+        for (int i = 0; i < nparts; ++i) {
+          // own part + the following pairs' parts, always in this order: reproducible
+          const float* sq = src_ws + (size_t)(2 * i) * tile_floats + (size_t)c0 * TILE_N;
           float f[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) f[j] = (c0 + j < rows) ? __ldcg(sq + (size_t)j * TILE_N) : 0.0f;
@@ -462,8 +473,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_act, const __grid_con
       if (lane == 0) {
         if (rank == 0) mbar_arrive(bar(BAR_ACC_EMPTY));
         else mbar_arrive_remote(acc_empty_leader);
-        // the warp that completes the slot's count (4 writers + 4 readers) puts the flag back to zero
-        if (role == 2 && atomicAdd(p.ws_flags + src_slot, 1u) == (unsigned)(2 * kNumEpiWarps - 1)) p.ws_flags[src_slot] = 0u;
+        // the warp that completes a slot's count (4 writers + 4 readers) puts the flag back to zero
+        for (int i = 0; i < nparts; ++i)
+          if (atomicAdd(p.ws_flags + src_slot + 2u * i, 1u) == (unsigned)(2 * kNumEpiWarps - 1)) p.ws_flags[src_slot + 2u * i] = 0u;
       }
       // staging -> global: one instruction moves four rows' 64-byte pieces
       const int n4 = n_tile * TILE_N + quarter * 32 + (lane & 7) * 4;  // first of this lane's 4 columns

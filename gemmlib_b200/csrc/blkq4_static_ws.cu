@@ -75,12 +75,11 @@ extern "C" int blkq4_fp16_gemm_static_ws_sm100(int block_size, bool column_wise_
                                                void const* offsets_ptr, size_t offsets_size, void* output_ptr,
                                                size_t output_size, void const* bias_ptr, size_t bias_size,
                                                unsigned flags, void* err) {
-  const size_t need = blkq4_gemm_workspace_size(m, n, k);
-  // A balanced plan (more tiles than SMs) that does not fit simply runs in whole rounds, as it would
-  // with no workspace; a split-K plan that does not fit is refused.
-  if (need > kStaticScratchBytes && !blkq4::gemm_tc_plan_balanced(m, n, k))
-    return fail(err, "Split-K workspace of " + std::to_string(need) + " bytes exceeds the static scratch of " +
-                         std::to_string(kStaticScratchBytes) + " bytes");
+  // A split-K plan of the one-CTA kernel that does not fit is refused.  Plans that only buy balance
+  // (balanced ranges of either kernel) are not: when they do not fit, the launch picks what fits.
+  if (blkq4::gemm_tc_split_plan_refusable(m, n, k, kStaticScratchBytes))
+    return fail(err, "Split-K workspace of " + std::to_string(blkq4_gemm_workspace_size(m, n, k)) +
+                         " bytes exceeds the static scratch of " + std::to_string(kStaticScratchBytes) + " bytes");
   std::string why;
   void* scratch = static_scratch(why);
   if (!scratch) return fail(err, "Static scratch unavailable: " + why);
