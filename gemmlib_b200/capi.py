@@ -36,6 +36,8 @@ SYMBOLS = (
     "blkq4_gather_destroy",
     "blkq4_gather_reset",
     "blkq4_gather_supported_sm100",
+    "blkq4_gemm_plan",
+    "blkq4_gemm_plan_range_bound",
     "blkq4_reset",
     "blkq4_version",
 )
@@ -82,6 +84,10 @@ def _load() -> ctypes.CDLL:
     lib.blkq4_gather_reset.restype = i
     lib.blkq4_gather_supported_sm100.argtypes = [i, ctypes.c_bool, i, i, i]
     lib.blkq4_gather_supported_sm100.restype = i
+    lib.blkq4_gemm_plan.argtypes = [i, i, i, sz, ctypes.POINTER(ctypes.c_int)]
+    lib.blkq4_gemm_plan.restype = i
+    lib.blkq4_gemm_plan_range_bound.argtypes = [i, i, i, i]
+    lib.blkq4_gemm_plan_range_bound.restype = i
     lib.blkq4_reset.argtypes = [vp]
     lib.blkq4_reset.restype = i
     lib.blkq4_gather_create.argtypes = [i, i, sz, ctypes.POINTER(vp), vp, vp]
@@ -173,6 +179,20 @@ def gather_supported(block_size: int, col_wise: bool, m: int, n_shard: int, k: i
     """Whether GatherContext.gemm takes the shape (fused GEMM + all-gather), else the caller computes
     locally and all-gathers with its own collective."""
     return bool(lib.blkq4_gather_supported_sm100(block_size, col_wise, m, n_shard, k))
+
+
+def gemm_plan(m: int, n: int, k: int, workspace_size: int = 0) -> dict:
+    """The work plan the tensor-core path would choose (host only; see blkq4_gemm_plan)."""
+    out = (ctypes.c_int * 6)()
+    if lib.blkq4_gemm_plan(m, n, k, workspace_size, out) != 0:
+        raise BlkQ4Error(f"no plan for {m}x{n}x{k}")
+    kernel = ("skinny", "one-cta", "pair")[out[0]]
+    return {"kernel": kernel, "rows_per_tile": out[1], "tiles": out[2], "split": out[3], "balanced": bool(out[4]),
+            "units": out[5]}
+
+
+def gemm_plan_range_bound(total_steps: int, k_steps: int, units: int, b: int) -> int:
+    return int(lib.blkq4_gemm_plan_range_bound(total_steps, k_steps, units, b))
 
 
 def static_scratch_size() -> int:

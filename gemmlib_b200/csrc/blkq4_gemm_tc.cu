@@ -915,3 +915,27 @@ int read_gemm_tc_error(cudaStream_t stream) {
 }
 
 }  // namespace blkq4
+
+extern "C" int blkq4_gemm_plan(int m, int n, int k, size_t workspace_size, int* out6) {
+  if (!out6 || m <= 0 || n <= 0 || k <= 0 || (k % 64) != 0) return -1;
+  for (int i = 0; i < 6; ++i) out6[i] = 0;
+  if (m <= 16) return 0;
+  const int sms = blkq4::sm_count() > 0 ? blkq4::sm_count() : 148;
+  const blkq4::PairPlan pp = blkq4::plan_pair(m, n, k, workspace_size);
+  if (pp.use) {
+    out6[0] = 2; out6[1] = pp.BM; out6[2] = pp.items; out6[3] = 1; out6[4] = pp.balanced;
+    out6[5] = pp.balanced ? sms / 2 : 0;
+    return 0;
+  }
+  const blkq4::SplitPlan sp = blkq4::plan_split(m, n, k, workspace_size);
+  const int bm = m >= 256 ? 256 : ((m + 15) / 16) * 16;
+  out6[0] = 1; out6[1] = bm; out6[2] = ((m + bm - 1) / bm) * ((n + blkq4::tc::TILE_N - 1) / blkq4::tc::TILE_N);
+  out6[3] = 1 << sp.split_shift; out6[4] = sp.balanced; out6[5] = sp.balanced ? sms : 0;
+  return 0;
+}
+
+extern "C" int blkq4_gemm_plan_range_bound(int total_steps, int k_steps, int units, int b) {
+  if (total_steps <= 0 || k_steps <= 0 || units <= 0 || b < 0 || b > units) return -1;
+  return blkq4::range_bound(total_steps, k_steps, units, b);
+}
+

@@ -149,6 +149,19 @@ int blkq4_fp16_gemm_sm100(
  * are unused, src/mickey/blk_q4/f16_gemm_sm80.h:86-90).
  */
 size_t blkq4_gemm_workspace_size(int m, int n, int k);
+
+/* No counterpart in the reference.  Host-only description of the work plan blkq4_fp16_gemm_ws_sm100 would
+ * choose for the problem with a workspace of `workspace_size` bytes: nothing is launched and no device is
+ * needed (the plan depends on the current device's SM count; 148 is assumed without a device).
+ *   out6[0]  kernel: 0 = skinny kernels (m <= 16), 1 = tensor-core kernel with one CTA per tile,
+ *            2 = tensor-core kernel with CTA pairs
+ *   out6[1]  activation rows per tile        out6[2]  output tiles
+ *   out6[3]  K split (1, 2 or 4)             out6[4]  1 when the tiles are cut in balanced k-step ranges
+ *   out6[5]  units the balanced ranges are cut for (SMs or pairs of SMs), else 0
+ * blkq4_gemm_plan_range_bound returns the first k step of unit b's range in the balanced plan's
+ * (tile, k step) sequence of total_steps = tiles * (k / 64) steps (b == units: the end). */
+int blkq4_gemm_plan(int m, int n, int k, size_t workspace_size, int* out6);
+int blkq4_gemm_plan_range_bound(int total_steps, int k_steps, int units, int b);
 int blkq4_fp16_gemm_ws_sm100(
   int block_size,
   bool column_wise_blocking,
