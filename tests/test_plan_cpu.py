@@ -60,3 +60,16 @@ def test_balanced_ranges_partition_the_steps(tiles, k_steps, units):
     for tile, u in heads.items():
         # the parts of a cut tile sit in consecutive units after the one that finishes it
         assert others[tile] == list(range(u + 1, u + 1 + len(others[tile])))
+
+
+def test_which_shapes_the_fused_all_gather_takes():
+    """blkq4_gather_supported_sm100 (per-rank shard shapes): decode and skinny shapes on the fast skinny
+    paths, prefill shapes with at least one round of pair tiles, nothing in between."""
+    assert capi.gather_supported(64, True, 1, 5504, 4096)        # decode kernel
+    assert capi.gather_supported(128, True, 16, 3584, 8192)      # TMA skinny kernel
+    assert not capi.gather_supported(32, True, 1, 4096, 4096)    # block 32: generic kernel
+    assert not capi.gather_supported(64, False, 4, 4096, 4096)   # row-wise blocks
+    assert not capi.gather_supported(64, True, 64, 14336, 8192)  # between the skinny and the pair kernel
+    assert capi.gather_supported(128, True, 4096, 3584, 8192)    # 16 x 14 pair tiles >= 74 pairs
+    assert not capi.gather_supported(128, True, 256, 3584, 8192)  # 14 pair tiles: not a round
+    assert not capi.gather_supported(64, True, 512, 4100, 4096)  # N not a multiple of 16
