@@ -112,10 +112,11 @@ template <bool COLWISE>
 __device__ __forceinline__ void dequant_step(const uint8_t* pk, const uint8_t* sc_tile, const uint8_t* zp_tile,
                                              int n_l, uint32_t nib_shift, int block, int block_shift, int has_zp,
                                              uint32_t (&out)[32]) {
+  const uint32_t rot_lo = nib_shift ? 30u : 6u, rot_hi = nib_shift ? 26u : 2u;
 #pragma unroll
   for (int c = 0; c < 4; ++c) {  // 16-byte chunk: k in [16 c, 16 c + 16)
     const uint4 wv = *reinterpret_cast<const uint4*>(pk + c * 16);
-    const uint32_t w4[4] = {wv.x >> nib_shift, wv.y >> nib_shift, wv.z >> nib_shift, wv.w >> nib_shift};
+    const uint32_t w4[4] = {wv.x, wv.y, wv.z, wv.w};
     // scale / offset half2 for the k pairs (2r, 2r+1) [lo] and (2r+8, 2r+9) [hi] of word r
     uint32_t s_lo[4], s_hi[4], o_lo[4], o_hi[4];
     if (COLWISE) {
@@ -154,10 +155,13 @@ __device__ __forceinline__ void dequant_step(const uint8_t* pk, const uint8_t* s
     }
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
-      // after the shift this thread's nibbles sit where column n0's do: bits 0-3 / 16-19 hold
-      // k = 2r, 2r+1 and bits 4-7 / 20-23 hold k = 2r+8, 2r+9; fp16(16 + q) by bit placement
-      const uint32_t h_lo = ((w4[r] << 6) & 0x03c003c0u) | 0x4c004c00u;
-      const uint32_t h_hi = ((w4[r] << 2) & 0x03c003c0u) | 0x4c004c00u;
+      // Column n0's nibbles sit at bits 0-3 / 16-19 (k = 2r, 2r+1) and 4-7 / 20-23 (k = 2r+8, 2r+9), column
+      // n0 + 8's eight bits further up; fp16(16 + q) by bit placement needs them at bits 6-9 / 22-25.  One
+      // rotation per operand does it (instead of a shift to this thread's nibbles and a second one into
+      // place): left by 6 / 2 for n0, by 30 / 26 (= right by 2 / 6) for n0 + 8; what wraps around falls
+      // outside the mask.
+      const uint32_t h_lo = (__funnelshift_l(w4[r], w4[r], rot_lo) & 0x03c003c0u) | 0x4c004c00u;
+      const uint32_t h_hi = (__funnelshift_l(w4[r], w4[r], rot_hi) & 0x03c003c0u) | 0x4c004c00u;
       const uint32_t d_lo = hfma2_u32(s_lo[r], h_lo, o_lo[r]);
       const uint32_t d_hi = hfma2_u32(s_hi[r], h_hi, o_hi[r]);
       // chunk c, word r: k = 16 c + 2 r (+1) -> column 8 c + r; k + 8 -> column 8 c + 4 + r
