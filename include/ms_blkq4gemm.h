@@ -143,9 +143,12 @@ int blkq4_fp16_gemm_sm100(
  * leaves it zeroed), used by one call at a time (calls on one stream may share it).  With it the
  * tensor-core kernel splits K when the output has too few 128 x 256 tiles to fill the GPU's SMs
  * (e.g. M = 512, N = 4096: 64 tiles on 148 SMs): parts of a tile's K range run on different SMs,
- * leave fp32 partial tiles in the workspace and the last part adds them in a fixed order.  A
- * null or too small workspace, or a size query of 0, means the call runs exactly as
- * blkq4_fp16_gemm_sm100.  No counterpart in the reference (its split-K template parameters
+ * leave fp32 partial tiles in the workspace and the last part adds them in a fixed order.  With
+ * more tiles than SMs (or than pairs of SMs, for m >= 256) but far from a whole number of rounds
+ * (e.g. 224 tiles on 148 SMs) it cuts the tiles' k steps in one balanced range per SM (or pair)
+ * instead, and a tile that straddles two ranges is finished through an fp32 partial tile in the same
+ * way.  Results are reproducible run to run with the same workspace size.  A null or too small
+ * workspace, or a size query of 0, means the call runs exactly as blkq4_fp16_gemm_sm100.  No counterpart in the reference (its split-K template parameters
  * are unused, src/mickey/blk_q4/f16_gemm_sm80.h:86-90).
  */
 size_t blkq4_gemm_workspace_size(int m, int n, int k);
@@ -179,9 +182,10 @@ int blkq4_fp16_gemm_ws_sm100(
 /**
  * blkq4_fp16_gemm_ws_sm100 with the workspace taken from a 12 MiB device array that is part of the
  * library (blkq4_static_scratch_size() bytes) instead of from the caller: nothing on this path
- * allocates, on the host or on the device.  A problem whose split-K workspace
- * (blkq4_gemm_workspace_size) would not fit is refused with an error (e.g. M = 256, N = K = 4096:
- * 32 tiles split four ways need 12.6 MB); use blkq4_fp16_gemm_sm100 for it.  Every call on a
+ * allocates, on the host or on the device.  A problem whose split-K workspace would not fit is
+ * refused with an error (e.g. M = 256, N = K = 4096: 32 tiles split four ways need 12.6 MB); use
+ * blkq4_fp16_gemm_sm100 for it.  A problem whose balanced-range workspace would not fit is not refused:
+ * it runs in whole rounds, as it would without a workspace.  Every call on a
  * device shares the one array, so calls that can overlap on the GPU - on different streams, or
  * replays of captured graphs running side by side - race and corrupt each other's results: one
  * call at a time per device.  If a bounded in-kernel wait expires (blkq4_last_kernel_status != 0),
